@@ -174,7 +174,8 @@ class CacheManager:
         for g in self.groups:
             shape = (len(g.entries), self.num_pages, g.need.kv_heads, self.page_size)
             g.k = torch.zeros(shape + (g.need.head_dim,), device=device, dtype=dtype)
-            g.v = torch.zeros(shape + (g.need.value_dim,), device=device, dtype=dtype)
+            # (a latent that keys and values share: the values are the start of the key rows, the view hands out the key pages)
+            g.v = g.k if g.need.values_in_keys else torch.zeros(shape + (g.need.value_dim,), device=device, dtype=dtype)
         # one slot more than there can be requests: the rows that pad a captured batch read and write the spare slot
         for i, need in self.state_needs.items():
             self.state[i] = torch.zeros((self.max_requests + 1, *need.shape), device=device, dtype=need.dtype)

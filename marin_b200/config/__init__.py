@@ -2,6 +2,7 @@
 from .base import ConfigError, ModelConfig, load_config, read_json
 from .fegarax import FegaraxConfig
 from .lakulix import LakulixConfig
+from .nirotar import NirotarConfig
 from .qwen3 import Qwen3Config
 
-__all__ = ["ConfigError", "FegaraxConfig", "LakulixConfig", "ModelConfig", "Qwen3Config", "load_config", "read_json"]
+__all__ = ["ConfigError", "FegaraxConfig", "LakulixConfig", "ModelConfig", "NirotarConfig", "Qwen3Config", "load_config", "read_json"]

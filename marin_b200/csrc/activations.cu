@@ -207,3 +207,23 @@ MB_API int mb_tanh_cap(void* x, int dtype, size_t total, float cap, cudaStream_t
     if (dtype == MB_BF16) return launch_kernel(tanh_kernel<bf16>, blocks_for(total, 256), 256, 0, s, 0, (bf16*)x, total, cap);
     return MB_ERR_BAD_DTYPE;
 }
+
+// ---- the square of relu, in place: x <- max(x, 0)^2 (the activation of a feed-forward without a gate) ----------------------
+template <typename T>
+__global__ void relu2_kernel(T* __restrict__ x, size_t total) {
+    PDL_ENTER();
+    x = pdl_fresh(x);
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; idx < total; idx += stride) {
+        const float v = fmaxf(to_f32(x[idx]), 0.0f);
+        x[idx] = from_f32<T>(v * v);
+    }
+}
+
+MB_API int mb_relu2(void* x, int dtype, size_t total, cudaStream_t s) {
+    if (total == 0) return 0;
+    if (dtype == MB_F32) return launch_kernel(relu2_kernel<float>, blocks_for(total, 256), 256, 0, s, 0, (float*)x, total);
+    if (dtype == MB_BF16) return launch_kernel(relu2_kernel<bf16>, blocks_for(total, 256), 256, 0, s, 0, (bf16*)x, total);
+    return MB_ERR_BAD_DTYPE;
+}

@@ -2,8 +2,10 @@
 //   * keys of `d` elements, values of `dv` (they may differ): K pages [page][kv_head][offset][d], V pages [..][dv];
 //   * which keys a position sees: all before it, the last `window`, or those of its own chunk of `chunk` positions
 //     (chunks counted from position 0 of the sequence, wherever a prompt was cut);
-//   * a sink: one more term in the softmax's denominator, a key of score 0 without a value,
-//         p_j = exp(s_j) / (1 + sum_j exp(s_j));
+//   * a sink: one more term in the softmax's denominator, a key without a value whose score is 0 or a learned number per
+//     query head (not scaled),  p_j = exp(s_j) / (exp(sink_h) + sum_j exp(s_j));
+//   * values that are the leading `dv` elements of the key rows (a latent shared by keys and values): the value pointer is
+//     the key pointer and `v_stride`, the distance between two positions' values, is the key rows' width;
 //   * an output gate: the result is multiplied element by element with sigmoid(g), g a column block of the fused
 //     projection.
 // This file holds the head preparation (biases, RMS norm of q and k per head or over the whole projection, partial
@@ -21,7 +23,8 @@
 // A row of `row` holds q (H heads of d), k (K heads of d), v (K heads of dv), then whatever follows (the gate's columns).
 // norm_mode 0: none; 1: per head over d, weight [d] shared by the heads; 2: over all of q (and all of k) at once, before
 // the split into heads, weight [H d] (and [K d]).  The first rot_dim elements of a head are rotated in pairs
-// (i, i + rot_dim/2) by the angle pos * inv_freq[i]; sines and cosines are multiplied by rot_mag.
+// (i, i + rot_dim/2), or (2i, 2i + 1) if `interleaved`, by the angle pos * inv_freq[i]; sines and cosines are multiplied by
+// rot_mag.
 // v_mode 0: values as they are; 1: they are also left in v_shared (activation dtype [tokens][K dv]) for later layers;
 // 2: v <- (1 - lam) v + lam v_shared, lam = *v_lambda, and the mixed values go to the cache.
 template <typename T>
@@ -30,7 +33,7 @@ __global__ void __launch_bounds__(1024) qkv_finish_kernel(
     const float* __restrict__ v_b, int norm_mode, const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
     const int* __restrict__ positions, const float* __restrict__ inv_freq, int rot_dim, float rot_mag,
     const int* __restrict__ slot_mapping, T* __restrict__ k_cache, T* __restrict__ v_cache, int v_mode, T* __restrict__ v_shared,
-    const float* __restrict__ v_lambda, int H, int K, int d, int dv, int page_size, int write_kv) {
+    const float* __restrict__ v_lambda, int H, int K, int d, int dv, int page_size, int write_kv, int interleaved) {
     PDL_ENTER();
     row = pdl_fresh(row); v_shared = pdl_fresh(v_shared);
     extern __shared__ float smem[];
@@ -97,8 +100,9 @@ __global__ void __launch_bounds__(1024) qkv_finish_kernel(
         for (int i = lane; i < d; i += 32) {
             float a = hv[i] * factor * (w != nullptr ? w[i] : 1.0f);
             if (i < rot_dim) {                                 // (rot_dim is 0 without a rotation)
-                const bool low = i < half;
-                const int j = low ? i : i - half, other = low ? i + half : i - half;
+                const bool low = interleaved ? (i & 1) == 0 : i < half;
+                const int j = interleaved ? i >> 1 : low ? i : i - half;
+                const int other = interleaved ? i ^ 1 : low ? i + half : i - half;
                 const float b = hv[other] * factor * (w != nullptr ? w[other] : 1.0f);
                 const float cs = cs_tab[j], sn = cs_tab[half + j];
                 a = low ? a * cs - b * sn : a * cs + b * sn;
@@ -151,7 +155,7 @@ __global__ void __launch_bounds__(RUNS <= 2 ? 1024 : 256) qkv_finish_vec_kernel(
     const float* __restrict__ v_b, int norm_mode, const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
     const int* __restrict__ positions, const float* __restrict__ inv_freq, int rot_dim, float rot_mag,
     const int* __restrict__ slot_mapping, bf16* __restrict__ k_cache, bf16* __restrict__ v_cache, int v_mode, bf16* __restrict__ v_shared,
-    const float* __restrict__ v_lambda, int H, int K, int d, int dv, int page_size, int write_kv) {
+    const float* __restrict__ v_lambda, int H, int K, int d, int dv, int page_size, int write_kv, int interleaved) {
     PDL_ENTER();
     row = pdl_fresh(row); v_shared = pdl_fresh(v_shared);
     extern __shared__ __align__(16) float smem[];
@@ -244,7 +248,16 @@ __global__ void __launch_bounds__(RUNS <= 2 ? 1024 : 256) qkv_finish_vec_kernel(
 #pragma unroll
             for (int e = 0; e < 8; ++e) a[e] = x[u][e] * factor;
         }
-        if (i0 < rot_dim) {
+        if (i0 < rot_dim && interleaved) {                     // partners are neighbours inside the run
+            const float4 c4 = *reinterpret_cast<const float4*>(cs_tab + (i0 >> 1)), s4 = *reinterpret_cast<const float4*>(cs_tab + half + (i0 >> 1));
+            const float cs[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float u = a[2 * e], v = a[2 * e + 1];
+                a[2 * e] = u * cs[e] - v * sn[e];
+                a[2 * e + 1] = v * cs[e] + u * sn[e];
+            }
+        } else if (i0 < rot_dim) {
             const bool low = i0 < half;
             const int j0 = low ? i0 : i0 - half, other = low ? i0 + half : i0 - half;
             float b[8], cs[8], sn[8];
@@ -299,7 +312,8 @@ static bool aligned16(const void* p) { return (((uintptr_t)p) & 15) == 0; }
 MB_API int mb_qkv_finish(const void* row, int row_stride, int dtype, void* q_out, const float* q_b, const float* k_b, const float* v_b,
                          int norm_mode, const float* q_w, const float* k_w, float eps, const int* positions, const float* inv_freq,
                          int rot_dim, float rot_mag, const int* slot_mapping, void* k_cache, void* v_cache, int v_mode, void* v_shared,
-                         const float* v_lambda, int tokens, int H, int K, int d, int dv, int page_size, int write_kv, cudaStream_t s) {
+                         const float* v_lambda, int tokens, int H, int K, int d, int dv, int page_size, int write_kv, int interleaved,
+                         cudaStream_t s) {
     if (tokens <= 0) return 0;
     if (d <= 0 || dv <= 0 || H <= 0 || K <= 0 || rot_dim > d || (rot_dim & 1) || norm_mode < 0 || norm_mode > 2) return MB_ERR_BAD_SIZE;
     if ((v_mode == 1 || v_mode == 2) && v_shared == nullptr) return MB_ERR_BAD_SIZE;
@@ -308,7 +322,7 @@ MB_API int mb_qkv_finish(const void* row, int row_stride, int dtype, void* q_out
     const size_t smem = ((size_t)(H + K) * d + rot_dim + H + K) * sizeof(float);
     if (smem > 160 * 1024) return MB_ERR_BAD_SIZE;
     const int runs8 = (H + K) * d / 8;
-    if (dtype == MB_BF16 && d % 8 == 0 && dv % 8 == 0 && (rot_dim / 2) % 8 == 0 && row_stride % 8 == 0 && runs8 <= 1024 * 2 &&
+    if (dtype == MB_BF16 && d % 8 == 0 && dv % 8 == 0 && (interleaved ? rot_dim % 8 == 0 : (rot_dim / 2) % 8 == 0) && row_stride % 8 == 0 && runs8 <= 1024 * 2 &&
         aligned16(row) && aligned16(q_out) && aligned16(q_b) && aligned16(k_b) && aligned16(v_b) && aligned16(q_w) && aligned16(k_w) &&
         aligned16(k_cache) && aligned16(v_cache) && aligned16(v_shared)) {
 #define QV_LAUNCH(RUNS, threads)                                                                                                        \
@@ -319,7 +333,7 @@ MB_API int mb_qkv_finish(const void* row, int row_stride, int dtype, void* q_out
         }                                                                                                                               \
         return launch_kernel(qkv_finish_vec_kernel<RUNS>, tokens, threads, smem, s, 0, (const bf16*)row, row_stride, (bf16*)q_out, q_b, k_b, \
                              v_b, norm_mode, q_w, k_w, eps, positions, inv_freq, rot_dim, rot_mag, slot_mapping, (bf16*)k_cache,         \
-                             (bf16*)v_cache, v_mode, (bf16*)v_shared, v_lambda, H, K, d, dv, page_size, write_kv);                       \
+                             (bf16*)v_cache, v_mode, (bf16*)v_shared, v_lambda, H, K, d, dv, page_size, write_kv, interleaved);          \
     } while (0)
         const int quarter = (((runs8 + 3) / 4 + 31) / 32) * 32;
         if (tokens >= 512 && quarter <= 256) QV_LAUNCH(4, quarter < 64 ? 64 : quarter);
@@ -336,7 +350,7 @@ MB_API int mb_qkv_finish(const void* row, int row_stride, int dtype, void* q_out
         }                                                                                                                            \
         return launch_kernel(qkv_finish_kernel<TT>, tokens, (H + K) * d < 4096 ? QF_THREADS : tokens <= 64 ? 1024 : 512, smem, s, 0, (const TT*)row, row_stride, (TT*)q_out, q_b, k_b, \
                              v_b, norm_mode, q_w, k_w, eps, positions, inv_freq, rot_dim, rot_mag, slot_mapping, (TT*)k_cache,      \
-                             (TT*)v_cache, v_mode, (TT*)v_shared, v_lambda, H, K, d, dv, page_size, write_kv);                       \
+                             (TT*)v_cache, v_mode, (TT*)v_shared, v_lambda, H, K, d, dv, page_size, write_kv, interleaved);          \
     } while (0)
     if (dtype == MB_F32) QF_LAUNCH(float);
     if (dtype == MB_BF16) QF_LAUNCH(bf16);
@@ -352,8 +366,8 @@ template <typename T>
 __global__ void __launch_bounds__(SK_THREADS) attention_sink_kernel(
     const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache, T* __restrict__ out,
     const int* __restrict__ block_table, int max_pages, const int* __restrict__ req_index, const int* __restrict__ positions,
-    int H, int K, int d, int dv, int page_size, float scale, int window, int chunk, int sink, const T* __restrict__ gate,
-    int gate_stride) {
+    int H, int K, int d, int dv, int page_size, float scale, int window, int chunk, int sink, const float* __restrict__ sink_logit,
+    int v_stride, const T* __restrict__ gate, int gate_stride) {
     PDL_ENTER();
     q = pdl_fresh(q); k_cache = pdl_fresh(k_cache); v_cache = pdl_fresh(v_cache); gate = pdl_fresh(gate);
     extern __shared__ float smem[];
@@ -371,8 +385,9 @@ __global__ void __launch_bounds__(SK_THREADS) attention_sink_kernel(
     for (int i = threadIdx.x; i < d; i += SK_THREADS) qs[i] = to_f32(qrow[i]);
     __syncthreads();
 
-    // the sink is a key of score 0 whose value is zero: the running maximum starts at 0 and the sum at 1
-    float m = sink ? 0.0f : -INFINITY, l = sink ? 1.0f : 0.0f;
+    // the sink is a key whose value is zero: the running maximum starts at its score (0 or the head's learned number) and
+    // the sum at 1
+    float m = sink ? (sink_logit != nullptr ? sink_logit[head] : 0.0f) : -INFINITY, l = sink ? 1.0f : 0.0f;
     float acc[SK_MAX_PER_THREAD];
 #pragma unroll
     for (int r = 0; r < SK_MAX_PER_THREAD; ++r) acc[r] = 0.0f;
@@ -405,7 +420,7 @@ __global__ void __launch_bounds__(SK_THREADS) attention_sink_kernel(
                 for (int j = 0; j < count; ++j) {
                     const int kj = base + j;
                     const size_t page = (size_t)table[kj / page_size];
-                    const T* vrow = v_cache + ((page * K + kh) * page_size + (size_t)(kj % page_size)) * dv;
+                    const T* vrow = v_cache + ((page * K + kh) * page_size + (size_t)(kj % page_size)) * v_stride;
                     a = fmaf(ps[j], to_f32(vrow[dd]), a);
                 }
                 acc[r] = a;
@@ -427,11 +442,14 @@ __global__ void __launch_bounds__(SK_THREADS) attention_sink_kernel(
 }
 
 // gate: null, or the first gate column of token 0 (rows `gate_stride` elements apart, H heads of dv side by side).
+// sink_logit: null (a sink of score 0, if `sink`) or a float32 score per query head.  v_stride: elements between the values of
+// two positions of a page (dv for value pages of their own; the key rows' width where values are the start of the key rows).
 MB_API int mb_attention_sink(const void* q, const void* k_cache, const void* v_cache, void* out, int dtype, const int* block_table,
                              int max_pages, const int* req_index, const int* positions, int tokens, int H, int K, int d, int dv,
-                             int page_size, float scale, int window, int chunk, int sink, const void* gate, int gate_stride,
-                             cudaStream_t s) {
+                             int page_size, float scale, int window, int chunk, int sink, const float* sink_logit, int v_stride,
+                             const void* gate, int gate_stride, cudaStream_t s) {
     if (tokens <= 0) return 0;
+    if (v_stride < dv) return MB_ERR_BAD_SIZE;
     if (d <= 0 || dv <= 0 || dv > SK_THREADS * SK_MAX_PER_THREAD || K <= 0 || H % K != 0 || window < 0 || chunk < 0) return MB_ERR_BAD_SIZE;
     dim3 grid(tokens, H);
     const size_t smem = (size_t)(d + SK_THREADS + 32) * sizeof(float);
@@ -439,10 +457,10 @@ MB_API int mb_attention_sink(const void* q, const void* k_cache, const void* v_c
     if (dtype == MB_F32)
         return launch_kernel(attention_sink_kernel<float>, grid, SK_THREADS, smem, s, 0, (const float*)q, (const float*)k_cache,
                              (const float*)v_cache, (float*)out, block_table, max_pages, req_index, positions, H, K, d, dv, page_size,
-                             scale, window, chunk, sink, (const float*)gate, gate_stride);
+                             scale, window, chunk, sink, sink_logit, v_stride, (const float*)gate, gate_stride);
     if (dtype == MB_BF16)
         return launch_kernel(attention_sink_kernel<bf16>, grid, SK_THREADS, smem, s, 0, (const bf16*)q, (const bf16*)k_cache,
                              (const bf16*)v_cache, (bf16*)out, block_table, max_pages, req_index, positions, H, K, d, dv, page_size,
-                             scale, window, chunk, sink, (const bf16*)gate, gate_stride);
+                             scale, window, chunk, sink, sink_logit, v_stride, (const bf16*)gate, gate_stride);
     return MB_ERR_BAD_DTYPE;
 }

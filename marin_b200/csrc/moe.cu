@@ -1,5 +1,7 @@
 // A routed feed-forward (mixture of experts): a router scores every expert for every token, the `top` best are chosen,
-// and the token goes through those experts only.  Expert: down( silu(gate x) * (up x) ), no biases.
+// and the token goes through those experts only.  Expert: down( silu(gate x) * (up x) ), no biases; or, `act_mode` 1, an
+// expert without a gate, down( relu(up x)^2 ), whose first matrix is [experts][ff][h].  Instead of a router a table may
+// name every token id's experts (mb_moe_table_route): the choice then depends on the token alone, with equal weights.
 //   * router: z = W_r h in float32, score = sigmoid(z) or the softmax of z over the experts; the chosen experts' scores are
 //     the weights, renormalised to sum 1 over the chosen ones if asked;
 //   * the weight multiplies the expert's input (x = w h, the activation sees it) or its output (x = h, result times w).
@@ -124,6 +126,29 @@ MB_API int mb_moe_route(const void* h_rows, int dtype, const float* router, int*
     return MB_ERR_BAD_DTYPE;
 }
 
+// ---- experts named by a table over the token ids: expert_out[t][c] = table[ids[t]][c], every weight 1 / top ------------------
+__global__ void moe_table_route_kernel(const int* __restrict__ ids, const int* __restrict__ table, int* __restrict__ expert_out,
+                                       float* __restrict__ weight_out, int tokens, int top, int vocab, int E) {
+    PDL_ENTER();
+    ids = pdl_fresh(ids);
+    const int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= tokens * top) return;
+    const int t = p / top, c = p - t * top;
+    int id = ids[t];
+    id = id < 0 ? 0 : id >= vocab ? vocab - 1 : id;
+    int e = table[(size_t)id * top + c];
+    e = e < 0 ? 0 : e >= E ? E - 1 : e;                         // a table from a damaged file stays inside the experts
+    expert_out[p] = e;
+    weight_out[p] = 1.0f / (float)top;
+}
+
+MB_API int mb_moe_table_route(const int* ids, const int* table, int* expert_out, float* weight_out, int tokens, int top, int vocab, int E,
+                              cudaStream_t s) {
+    if (tokens <= 0) return 0;
+    if (top <= 0 || vocab <= 0 || E <= 0) return MB_ERR_BAD_SIZE;
+    return launch_kernel(moe_table_route_kernel, (tokens * top + 127) / 128, 128, 0, s, 0, ids, table, expert_out, weight_out, tokens, top, vocab, E);
+}
+
 // ---- pairs grouped by expert: offsets[E + 1] and order[pairs] (the pairs of expert e are order[offsets[e] .. offsets[e+1])) ----
 // One block.  Within an expert the pairs come in no fixed order: no result depends on it.
 __global__ void __launch_bounds__(1024) moe_group_kernel(const int* __restrict__ expert_of, int pairs, int E, int* __restrict__ offsets,
@@ -160,7 +185,7 @@ template <typename T>
 __global__ void __launch_bounds__(ME_THREADS) moe_gate_up_kernel(const T* __restrict__ h_rows, const T* __restrict__ w_gate_up,
                                                                  const int* __restrict__ expert_of, const float* __restrict__ weight_of,
                                                                  T* __restrict__ act, int h, int ff, int top, int weight_on_input,
-                                                                 int interleaved) {
+                                                                 int interleaved, int act_mode) {
     PDL_ENTER();
     h_rows = pdl_fresh(h_rows); expert_of = pdl_fresh(expert_of); weight_of = pdl_fresh(weight_of);
     extern __shared__ float x[];               // [h]
@@ -171,6 +196,17 @@ __global__ void __launch_bounds__(ME_THREADS) moe_gate_up_kernel(const T* __rest
     for (int i = threadIdx.x; i < h; i += ME_THREADS) x[i] = to_f32(from_f32<T>(to_f32(h_rows[(size_t)token * h + i]) * wgt));
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (act_mode == 1) {                                       // no gate: relu(up x)^2
+        const T* only = w_gate_up + (size_t)e * ff * h;
+        for (int c = warp; c < ff; c += ME_THREADS / 32) {
+            const T* u = only + (size_t)c * h;
+            float du = 0.0f;
+            for (int i = lane; i < h; i += 32) du = fmaf(x[i], to_f32(u[i]), du);
+            du = fmaxf(warp_sum(du), 0.0f);
+            if (lane == 0) act[(size_t)p * ff + c] = from_f32<T>(du * du);
+        }
+        return;
+    }
     const T* base = w_gate_up + (size_t)e * 2 * ff * h;
     for (int c = warp; c < ff; c += ME_THREADS / 32) {
         const T* g = base + (size_t)gate_up_row(c, 0, ff, interleaved) * h;
@@ -215,20 +251,20 @@ __global__ void __launch_bounds__(ME_THREADS) moe_down_kernel(const T* __restric
 // which = 0: act <- the activations of every pair; which = 1: y += the chosen experts' outputs, from act.
 MB_API int mb_moe_experts_plain(const void* h_rows, int dtype, const void* w_gate_up, const void* w_down, const int* expert_of,
                                 const float* weight_of, void* act, float* y, int tokens, int h, int ff, int top, int weight_on_input,
-                                int interleaved, int which, cudaStream_t s) {
+                                int interleaved, int which, int act_mode, cudaStream_t s) {
     if (tokens <= 0) return 0;
     if (h <= 0 || ff <= 0 || top <= 0 || (size_t)h * 4 > 48 * 1024 || (size_t)ff * 4 > 48 * 1024) return MB_ERR_BAD_SIZE;
     if (dtype == MB_F32) {
         if (which == 0)
             return launch_kernel(moe_gate_up_kernel<float>, tokens * top, ME_THREADS, (size_t)h * 4, s, 0, (const float*)h_rows,
-                                 (const float*)w_gate_up, expert_of, weight_of, (float*)act, h, ff, top, weight_on_input, interleaved);
+                                 (const float*)w_gate_up, expert_of, weight_of, (float*)act, h, ff, top, weight_on_input, interleaved, act_mode);
         return launch_kernel(moe_down_kernel<float>, tokens, ME_THREADS, (size_t)ff * 4, s, 0, (const float*)act, (const float*)w_down,
                              expert_of, weight_of, y, h, ff, top, weight_on_input);
     }
     if (dtype == MB_BF16) {
         if (which == 0)
             return launch_kernel(moe_gate_up_kernel<bf16>, tokens * top, ME_THREADS, (size_t)h * 4, s, 0, (const bf16*)h_rows,
-                                 (const bf16*)w_gate_up, expert_of, weight_of, (bf16*)act, h, ff, top, weight_on_input, interleaved);
+                                 (const bf16*)w_gate_up, expert_of, weight_of, (bf16*)act, h, ff, top, weight_on_input, interleaved, act_mode);
         return launch_kernel(moe_down_kernel<bf16>, tokens, ME_THREADS, (size_t)ff * 4, s, 0, (const bf16*)act, (const bf16*)w_down,
                              expert_of, weight_of, y, h, ff, top, weight_on_input);
     }
@@ -251,6 +287,7 @@ MB_API int mb_moe_experts_plain(const void* h_rows, int dtype, const void* w_gat
 // stages of the cp.async ring: the down product has one weight tile per stage and few CTAs when few experts are chosen, so it
 // keeps more stages in flight
 #define G_STAGES_OF(MODE) ((MODE) == 0 ? 4 : 6)
+#define G_NB_OF(MODE) ((MODE) == 0 ? 2 : 1)
 
 template <typename T>
 __global__ void moe_gather_kernel(const T* __restrict__ h_rows, const int* __restrict__ order, const float* __restrict__ weight_of,
@@ -269,6 +306,7 @@ __global__ void moe_gather_kernel(const T* __restrict__ h_rows, const int* __res
 
 // MODE 0: W [E][2 N][K] (gate rows, then up rows), result silu(gate) * up as bf16 [rows][N].
 // MODE 1: W [E][N][K], result float32: row r goes to dst_rows[r] (null: r), times row_scale[r] (null: 1), added if `accumulate`.
+// MODE 2: W [E][N][K] (experts without a gate), result relu(.)^2 as bf16 [rows][N].
 // GMT: pairs per tile, 16, 32 or 64.  The four warps take 16 rows each where the tile has 64, two row groups x two column
 // groups where it has 32, four column groups of 16 where it has 16: with few pairs per expert (single-token steps) a tile of
 // 64 rows would spend the tensor pipe on rows that hold nothing (measured: 45 % of its cycles on 2 live rows of 64).
@@ -279,7 +317,7 @@ __global__ void __launch_bounds__(128) moe_grouped_kernel(const bf16* __restrict
                                                           const float* __restrict__ row_scale, int accumulate, int interleaved) {
     PDL_ENTER();
     A = pdl_fresh(A); offsets = pdl_fresh(offsets); dst_rows = pdl_fresh(dst_rows); row_scale = pdl_fresh(row_scale); f_out = pdl_fresh(f_out);
-    constexpr int NB = MODE == 0 ? 2 : 1;
+    constexpr int NB = G_NB_OF(MODE);
     constexpr int G_STAGES = G_STAGES_OF(MODE);
     constexpr int WR = GMT / 16, WC = 4 / WR, NT = (GN / 8) / WC;       // row groups, column groups, 8-column tiles per warp
     extern __shared__ __align__(16) uint8_t g_smem[];
@@ -378,6 +416,16 @@ __global__ void __launch_bounds__(128) moe_grouped_kernel(const bf16* __restrict
                     *reinterpret_cast<uint32_t*>(dst + c) = pack_bf16(g0 / (1.0f + __expf(-g0)) * u0, g1 / (1.0f + __expf(-g1)) * u1);
                 }
             }
+        } else if (MODE == 2) {
+            bf16* dst = act_out + (size_t)row * N;
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                const int c = col + j * 8;
+                if (c < N) {
+                    const float u0 = fmaxf(acc[0][j][2 * rr], 0.0f), u1 = fmaxf(acc[0][j][2 * rr + 1], 0.0f);
+                    *reinterpret_cast<uint32_t*>(dst + c) = pack_bf16(u0 * u0, u1 * u1);
+                }
+            }
         } else {
             const size_t to = dst_rows != nullptr ? (size_t)dst_rows[row] : (size_t)row;
             const float f = row_scale != nullptr ? row_scale[row] : 1.0f;
@@ -411,7 +459,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ rows, const int* __
     }
 }
 
-#define G_SMEM(MODE, GMT) (G_STAGES_OF(MODE) * ((GMT) + ((MODE) == 0 ? 2 : 1) * GN) * GLD * 2)
+#define G_SMEM(MODE, GMT) (G_STAGES_OF(MODE) * ((GMT) + G_NB_OF(MODE) * GN) * GLD * 2)
 
 // Whether the tensor-core path takes these sizes: both inner sizes in whole steps of 64, rows 16-byte aligned.
 MB_API int mb_moe_fast_supported(int h, int ff) { return h % GK == 0 && ff % GK == 0 && h % 8 == 0 && ff % 8 == 0; }
@@ -447,11 +495,13 @@ MB_API int mb_moe_gather(const void* h_rows, const int* order, const float* weig
                          weight_sorted, inv, h, top, weight_on_input);
 }
 
-// act bf16 [pairs][ff] = silu(gate xs) * (up xs), expert by expert.
+// act bf16 [pairs][ff] = silu(gate xs) * (up xs), expert by expert; act_mode 1: relu(up xs)^2 with w_gate_up = [E][ff][h].
 MB_API int mb_moe_grouped_gate_up(const void* xs, const void* w_gate_up, const int* offsets, void* act, int pairs, int h, int ff, int E,
-                                  int interleaved, cudaStream_t s) {
+                                  int interleaved, int act_mode, cudaStream_t s) {
     if (pairs <= 0) return 0;
     if (!mb_moe_fast_supported(h, ff) || E <= 0) return MB_ERR_BAD_SIZE;
+    if (act_mode == 1)
+        return grouped_by_rows<2>((const bf16*)xs, (const bf16*)w_gate_up, offsets, E, ff, h, (bf16*)act, nullptr, nullptr, nullptr, 0, 0, pairs, s);
     return grouped_by_rows<0>((const bf16*)xs, (const bf16*)w_gate_up, offsets, E, ff, h, (bf16*)act, nullptr, nullptr, nullptr, 0, interleaved,
                               pairs, s);
 }

@@ -157,6 +157,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "mb_attention_sigmoid": ["attention_sigmoid.cu"],
     "mb_hyper": ["hyper.cu"],
     "mb_attention_sink": ["attention_sink.cu"],
+    "mb_attention_latent": ["attention_latent.cu"],
     "mb_moe": ["moe.cu"],
     "mb_host": ["host/cache_core.cpp", "host/scheduler.cpp", "host/sampler.cpp", "host/safetensors.cpp"],
 }

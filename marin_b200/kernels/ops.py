@@ -768,6 +768,15 @@ def gemm_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor, out: torch.Tensor,
                                                 _c_int(bn), _c_int(1), _ptr(s.error), _stream()), "gemm+swiglu (tensor cores)")
 
 
+def gemm_act(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, activation: str = "relu2") -> None:
+    """``out = act(x w^T)`` in the activation dtype, for a feed-forward without a gate (``activation`` "relu2": the square of
+    relu).  The product, then the activation in place over its result."""
+    if activation != "relu2":
+        raise KernelError(f"gemm_act: unknown activation {activation!r}")
+    gemm(x, w, out)
+    relu2(out)
+
+
 def gather_rows(src: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
     _need_cuda(src, rows, out)
     W, h = out.shape
@@ -889,6 +898,13 @@ def tanh_cap(x: torch.Tensor, cap: float) -> None:
     _need_cuda(x)
     _cost(2 * _size(x), 2.0 * x.numel())
     _check(_lib("mb_activations").mb_tanh_cap(_ptr(x), _code(x), _c_size_t(x.numel()), _c_float(cap), _stream()), "tanh cap")
+
+
+def relu2(x: torch.Tensor) -> None:
+    """``x <- max(x, 0)^2`` in place: the activation of a feed-forward without a gate."""
+    _need_cuda(x)
+    _cost(2 * _size(x), 2.0 * x.numel())
+    _check(_lib("mb_activations").mb_relu2(_ptr(x), _code(x), _c_size_t(x.numel()), _stream()), "relu squared")
 
 
 # ---- recurrences with a matrix state per head (csrc/recurrent.cu) ------------------------------------------------------
@@ -1181,11 +1197,11 @@ VALUE_MODES = {None: 0, "leave": 1, "mix": 2}
 
 def qkv_finish(rows: torch.Tensor, q_out: torch.Tensor, q_b, k_b, v_b, norm: Optional[str], q_w, k_w, eps: float, positions,
                inv_freq, rot_dim: int, rot_mag: float, slot_mapping, k_cache, v_cache, value_mode: Optional[str], v_shared,
-               v_lambda, H: int, K: int, d: int, dv: int, write_kv: bool = True) -> None:
+               v_lambda, H: int, K: int, d: int, dv: int, write_kv: bool = True, interleaved: bool = False) -> None:
     """Finishes the heads of a fused projection whose rows hold q | k | v (| more columns that are left alone): biases, the
     RMS norm of q and k (``norm`` "head": per head with a weight ``[d]``; "whole": over the whole of q, and of k, with weights
-    ``[H d]`` / ``[K d]``), the rotation of the first ``rot_dim`` elements of each head (half-split pairs, sines and cosines
-    times ``rot_mag``), and the values: as they are, also left in ``v_shared`` ("leave"), or mixed with what ``v_shared`` holds,
+    ``[H d]`` / ``[K d]``), the rotation of the first ``rot_dim`` elements of each head (half-split pairs, or neighbours
+    ``(2i, 2i + 1)`` if ``interleaved``; sines and cosines times ``rot_mag``), and the values: as they are, also left in ``v_shared`` ("leave"), or mixed with what ``v_shared`` holds,
     ``(1 - lam) v + lam v_shared`` ("mix").  Queries go to ``q_out``, keys and values into their pages."""
     _need_cuda(rows, q_out, q_b, k_b, v_b, q_w, k_w, positions, inv_freq, slot_mapping, k_cache, v_cache, v_shared, v_lambda)
     T = rows.shape[0]
@@ -1198,20 +1214,27 @@ def qkv_finish(rows: torch.Tensor, q_out: torch.Tensor, q_b, k_b, v_b, norm: Opt
         _ptr(rows), _c_int(rows.shape[1]), _code(rows), _ptr(q_out), _ptr(q_b), _ptr(k_b), _ptr(v_b), _c_int(NORM_MODES[norm]), _ptr(q_w),
         _ptr(k_w), _c_float(eps), _ptr(positions), _ptr(inv_freq), _c_int(rot_dim if inv_freq is not None else 0), _c_float(rot_mag),
         _ptr(slot_mapping), _ptr(k_cache), _ptr(v_cache), _c_int(VALUE_MODES[value_mode]), _ptr(v_shared), _ptr(v_lambda), _c_int(T),
-        _c_int(H), _c_int(K), _c_int(d), _c_int(dv), _c_int(page_size), _c_int(int(write_kv)), _stream()), "q|k|v heads (sink attention)")
+        _c_int(H), _c_int(K), _c_int(d), _c_int(dv), _c_int(page_size), _c_int(int(write_kv)), _c_int(int(interleaved)), _stream()),
+        "q|k|v heads (sink attention)")
 
 
 def attention_sink(q, k_cache, v_cache, out, ctx, block_table, H: int, K: int, d: int, dv: int, scale: float, window: int = 0,
-                   chunk: int = 0, sink: bool = True, gate: Optional[torch.Tensor] = None, plan=None) -> None:
+                   chunk: int = 0, sink: bool = True, gate: Optional[torch.Tensor] = None, plan=None,
+                   sink_logits: Optional[torch.Tensor] = None) -> None:
     """Causal softmax attention of the step's tokens over the paged cache.  A position sees the keys before it (its own
     included), of them only the last ``window`` (0: all) and only those of its own chunk of ``chunk`` positions (0: no
-    chunks).  ``sink``: one is added to the softmax's denominator.  ``gate`` (activation dtype, a view ``[T, H dv]`` whose rows
-    may be strided): the result is multiplied by ``sigmoid(gate)``."""
-    _need_cuda(q, k_cache, v_cache, out, block_table)
+    chunks).  ``sink``: ``exp(sink_logits[head])`` is added to the softmax's denominator (float32 ``[H]``, not scaled; None: a
+    score of 0, so one is added).  ``gate`` (activation dtype, a view ``[T, H dv]`` whose rows may be strided): the result is
+    multiplied by ``sigmoid(gate)``.  ``v_cache`` may be ``k_cache`` itself: the values are then the first ``dv`` elements
+    of the key rows (a latent that keys and values share)."""
+    _need_cuda(q, k_cache, v_cache, out, block_table, sink_logits)
     T = q.shape[0]
     page_size = k_cache.shape[2]
+    values_in_keys = v_cache.data_ptr() == k_cache.data_ptr()
     assert tuple(q.shape) == (T, H * d) and tuple(out.shape) == (T, H * dv) and k_cache.dtype == q.dtype and v_cache.dtype == q.dtype
-    assert k_cache.shape[3] == d and v_cache.shape[3] == dv
+    assert k_cache.shape[3] == d and (v_cache.shape[3] == dv or (values_in_keys and dv <= d))
+    assert sink_logits is None or (sink and sink_logits.dtype == torch.float32 and sink_logits.numel() == H)
+    v_stride = d if values_in_keys else dv
     gate_stride = 0
     if gate is not None:
         assert gate.is_cuda and gate.dtype == q.dtype and tuple(gate.shape) == (T, H * dv) and gate.stride(1) == 1
@@ -1220,7 +1243,8 @@ def attention_sink(q, k_cache, v_cache, out, ctx, block_table, H: int, K: int, d
         return
     size = q.element_size()
     per_row = H * (d + (3 if gate is not None else 2) * dv) * size
-    if use_fast_sink_attention and fast_sink_attention_supported(q.dtype, H, K, d, dv) and page_size & (page_size - 1) == 0:
+    if (use_fast_sink_attention and fast_sink_attention_supported(q.dtype, H, K, d, dv) and page_size & (page_size - 1) == 0
+            and not values_in_keys and sink_logits is None):
         lib = _sink_lib(d, dv, H // K)
         max_pages = block_table.shape[1]
         nd = ctx.num_decode
@@ -1267,7 +1291,7 @@ def attention_sink(q, k_cache, v_cache, out, ctx, block_table, H: int, K: int, d
     _check(_lib("mb_attention_sink").mb_attention_sink(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _code(q), _ptr(block_table), _c_int(block_table.shape[1]), _ptr(ctx.req_index),
         _ptr(ctx.positions), _c_int(T), _c_int(H), _c_int(K), _c_int(d), _c_int(dv), _c_int(page_size), _c_float(scale), _c_int(window),
-        _c_int(chunk), _c_int(int(sink)), _ptr(gate), _c_int(gate_stride), _stream()), "attention (sink)")
+        _c_int(chunk), _c_int(int(sink)), _ptr(sink_logits), _c_int(v_stride), _ptr(gate), _c_int(gate_stride), _stream()), "attention (sink)")
 
 
 #: bf16 sink attention goes to the tensor-core kernels where the head layout allows (False: always the plain kernel)
@@ -1287,10 +1311,12 @@ def _sink_lib(d: int, dv: int, group: int):
     return build.load(f"mb_attention_sink_fast_d{d}_v{dv}_g{group}", *_sink_job(d, dv, group))
 
 
-def sink_attention_jobs(dtype, H: int, K: int, d: int, dv: int) -> dict:
+def sink_attention_jobs(dtype, H: int, K: int, d: int, dv: int, values_in_keys: bool = False) -> dict:
     """The kernels a sink-attention mixer of this head layout runs: the head preparation and the plain kernel, and the
     tensor-core kernels compiled for the layout where it allows."""
     jobs = library_jobs("mb_attention_sink")
+    if values_in_keys:
+        return jobs
     if use_fast_sink_attention and fast_sink_attention_supported(dtype, H, K, d, dv):
         jobs[f"mb_attention_sink_fast_d{d}_v{dv}_g{H // K}"] = _sink_job(d, dv, H // K)
         if d == dv and d in (64, 128):
@@ -1314,11 +1340,12 @@ class SinkDecodePlan:
         self.split, self.chunks = int(split), int(chunks)
 
 
-def sink_decode_plan(dtype, requests: int, H: int, K: int, d: int, dv: int, span: int, window: int, chunk: int):
+def sink_decode_plan(dtype, requests: int, H: int, K: int, d: int, dv: int, span: int, window: int, chunk: int,
+                     values_in_keys: bool = False):
     """Enough chunks for about four CTAs per SM over all requests and kv heads, none shorter than 64 keys.  A token sees at
     most its window or its chunk of keys, whatever the sequence's length: the split follows that, not the context.  None
     where the plain kernel runs (it needs no plan)."""
-    if not (use_fast_sink_attention and fast_sink_attention_supported(dtype, H, K, d, dv)):
+    if values_in_keys or not (use_fast_sink_attention and fast_sink_attention_supported(dtype, H, K, d, dv)):
         return None
     seen = max(int(span), 1)
     if window > 0:
@@ -1332,6 +1359,44 @@ def sink_decode_plan(dtype, requests: int, H: int, K: int, d: int, dv: int, span
     least = SINK_DECODE_LEAST_SPLIT if longest > SINK_DECODE_LEAST_SPLIT else 64
     split = max(least, -(-(-(-longest // want)) // 64) * 64)
     return SinkDecodePlan(split, max(1, -(-longest // split)))
+
+
+# ---- attention over a latent that keys and values share (csrc/attention_latent.cu) -------------------------------------------
+def latent_finish(rows: torch.Tensor, q_out: torch.Tensor, c_weight, eps: float, positions, inv_freq, rot_dims: int, interleaved: bool,
+                  slot_mapping, k_cache, H: int, dn: int, dr: int, r: int, write_kv: bool = True) -> None:
+    """Finishes a fused projection whose rows hold ``H`` query heads of ``dn`` unrotated and ``dr`` rotated numbers and, for a
+    layer that owns its cache, ``r`` latent numbers and ``dr`` key numbers.  The queries' rotated parts go, rotated, to
+    ``q_out[:, head, r:]`` (``[T, H, r + dr]``; the first ``r`` of every head are left for ``heads_product``); the latent is
+    divided by its root mean square (times ``c_weight``) and written with the rotated key part into the page row ``[r + dr]``."""
+    _need_cuda(rows, q_out, c_weight, positions, inv_freq, slot_mapping, k_cache)
+    T = rows.shape[0]
+    D = r + dr
+    assert tuple(q_out.shape) == (T, H * D) and q_out.dtype == rows.dtype and rows.shape[1] >= H * (dn + dr) + (D if write_kv else 0)
+    assert not write_kv or (k_cache.dtype == rows.dtype and k_cache.shape[1] == 1 and k_cache.shape[3] == D and c_weight is not None)
+    _cost((rows.shape[1] - H * dn) * T * rows.element_size() + T * (H * dr + D) * rows.element_size(), 6.0 * T * (H * dr + D))
+    _check(_lib("mb_attention_latent").mb_latent_finish(
+        _ptr(rows), _c_int(rows.shape[1]), _code(rows), _ptr(q_out), _ptr(c_weight), _c_float(eps), _ptr(positions), _ptr(inv_freq),
+        _c_int(rot_dims if inv_freq is not None else 0), _c_int(int(interleaved)), _ptr(slot_mapping), _ptr(k_cache), _c_int(T), _c_int(H),
+        _c_int(dn), _c_int(dr), _c_int(r), _c_int(k_cache.shape[2] if write_kv else 0), _c_int(int(write_kv)), _stream()), "latent heads")
+
+
+#: bf16 products per head go to the tensor-core kernel where the layout allows (False: always the plain kernel)
+use_fast_heads_product = True
+
+
+def heads_product(x: torch.Tensor, x_head: int, K: int, w: torch.Tensor, out: torch.Tensor, o_head: int) -> None:
+    """A product per head over strided rows: ``out[t, a o_head + n] = sum_k w[a, n, k] x[t, a x_head + k]`` for every head ``a``
+    of ``w`` ``[H, N, K]``.  ``x`` and ``out`` are ``[T, row]`` tensors of which every head reads / writes a slice."""
+    _need_cuda(x, w, out)
+    T = x.shape[0]
+    H, N = w.shape[0], w.shape[1]
+    assert w.shape[2] == K and w.dtype == x.dtype == out.dtype and out.shape[0] == T
+    assert (H - 1) * x_head + K <= x.shape[1] and (H - 1) * o_head + N <= out.shape[1]
+    size = x.element_size()
+    _cost(_size(w) + T * H * (K + N) * size, 2.0 * T * H * N * K)
+    _check(_lib("mb_attention_latent").mb_heads_product(
+        _ptr(x), _c_int(x.shape[1]), _c_int(x_head), _ptr(w), _ptr(out), _c_int(out.shape[1]), _c_int(o_head), _code(x), _c_int(T), _c_int(H),
+        _c_int(N), _c_int(K), _c_int(int(use_fast_heads_product)), _stream()), "product per head")
 
 
 # ---- routed feed-forward ------------------------------------------------------------------------------------------------------
@@ -1352,6 +1417,18 @@ def moe_route(x: torch.Tensor, router: torch.Tensor, experts_out: torch.Tensor, 
                                       _c_int(top), _c_int(SCORE_MODES[score]), _c_int(int(renormalize)), _stream()), "router")
 
 
+def moe_table_route(token_ids: torch.Tensor, table: torch.Tensor, E: int, experts_out: torch.Tensor, weights_out: torch.Tensor) -> None:
+    """Experts named by a table over the token ids: ``experts_out[t] = table[token_ids[t]]`` (``[vocab, top]`` int32), every
+    weight ``1 / top``."""
+    _need_cuda(token_ids, table, experts_out, weights_out)
+    T, top = experts_out.shape
+    assert table.dtype == torch.int32 and table.shape[1] == top and token_ids.dtype == torch.int32 and token_ids.numel() == T
+    assert experts_out.dtype == torch.int32 and weights_out.dtype == torch.float32 and tuple(weights_out.shape) == (T, top)
+    _cost(_size(token_ids) + 3 * _size(experts_out))
+    _check(_lib("mb_moe").mb_moe_table_route(_ptr(token_ids), _ptr(table), _ptr(experts_out), _ptr(weights_out), _c_int(T), _c_int(top),
+                                            _c_int(table.shape[0]), _c_int(E), _stream()), "experts from the table")
+
+
 def moe_group(experts: torch.Tensor, E: int, offsets: torch.Tensor, order: torch.Tensor) -> None:
     """The (token, choice) pairs grouped by expert: ``order[offsets[e] : offsets[e + 1]]`` are expert ``e``'s pairs."""
     _need_cuda(experts, offsets, order)
@@ -1361,27 +1438,32 @@ def moe_group(experts: torch.Tensor, E: int, offsets: torch.Tensor, order: torch
     _check(_lib("mb_moe").mb_moe_group(_ptr(experts), _c_int(pairs), _c_int(E), _ptr(offsets), _ptr(order), _stream()), "pairs grouped")
 
 
+EXPERT_ACTIVATIONS = {"swiglu": 0, "relu2": 1}
+
+
 def moe_experts_plain(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, experts: torch.Tensor, weights: torch.Tensor,
-                      act: torch.Tensor, y: torch.Tensor, weight_on_input: bool, interleaved: bool = False) -> None:
+                      act: torch.Tensor, y: torch.Tensor, weight_on_input: bool, interleaved: bool = False, activation: str = "swiglu") -> None:
     """``y[t] += sum_c down_e( silu(gate_e x) * (up_e x) )`` over token ``t``'s chosen experts ``e`` in choice order, ``x = w h[t]``
     where the weight goes on the input, else the result times ``w``.  Any sizes, both dtypes.  ``interleaved``: an expert's
-    gate and up rows alternate in blocks of 16 (``interleave_gate_up``) instead of gate rows first."""
+    gate and up rows alternate in blocks of 16 (``interleave_gate_up``) instead of gate rows first.  ``activation`` "relu2":
+    experts without a gate, ``down_e( relu(up_e x)^2 )``, ``w_gate_up`` then holds the up matrices ``[E, ff, h]`` alone."""
     _need_cuda(x, w_gate_up, w_down, experts, weights, act, y)
     T, h = x.shape
     top = experts.shape[1]
     ff = w_down.shape[2]
-    assert tuple(w_gate_up.shape[1:]) == (2 * ff, h) and tuple(w_down.shape[1:]) == (h, ff) and w_gate_up.dtype == x.dtype == w_down.dtype
+    gated = activation == "swiglu"
+    assert tuple(w_gate_up.shape[1:]) == ((2 if gated else 1) * ff, h) and tuple(w_down.shape[1:]) == (h, ff) and w_gate_up.dtype == x.dtype == w_down.dtype
     assert act.dtype == x.dtype and act.numel() >= T * top * ff and y.dtype == torch.float32 and tuple(y.shape) == (T, h)
     pairs = T * top
     touched = min(pairs, w_down.shape[0])
     for which, what in ((0, "experts, gate|up"), (1, "experts, down")):
         if which == 0:
-            _cost(touched * 2 * ff * h * x.element_size() + _size(x) + pairs * ff * x.element_size(), 4.0 * pairs * ff * h)
+            _cost(touched * (2 if gated else 1) * ff * h * x.element_size() + _size(x) + pairs * ff * x.element_size(), (4.0 if gated else 2.0) * pairs * ff * h)
         else:
             _cost(touched * ff * h * x.element_size() + pairs * ff * x.element_size() + 2 * _size(y), 2.0 * pairs * ff * h)
         _check(_lib("mb_moe").mb_moe_experts_plain(_ptr(x), _code(x), _ptr(w_gate_up), _ptr(w_down), _ptr(experts), _ptr(weights), _ptr(act),
                                                   _ptr(y), _c_int(T), _c_int(h), _c_int(ff), _c_int(top), _c_int(int(weight_on_input)),
-                                                  _c_int(int(interleaved)), _c_int(which), _stream()), what)
+                                                  _c_int(int(interleaved)), _c_int(which), _c_int(EXPERT_ACTIVATIONS[activation]), _stream()), what)
 
 
 #: bf16 experts go to the grouped tensor-core kernels where the sizes allow (False: always the plain kernels)
@@ -1415,7 +1497,7 @@ def _expert_streams(device, n: int):
 
 
 def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, experts: torch.Tensor, weights: torch.Tensor,
-                y: torch.Tensor, weight_on_input: bool, workspace, interleaved: bool = False) -> None:
+                y: torch.Tensor, weight_on_input: bool, workspace, interleaved: bool = False, activation: str = "swiglu") -> None:
     """The chosen experts' outputs added into ``y`` (float32 ``[T, h]``); see ``moe_experts_plain``.  bf16 with sizes in steps
     of 64: the pairs are sorted by expert on the device and their inputs gathered in that order; then either two grouped
     products over all experts (few pairs: single-token steps, captured or not: nothing is read back), or, with many pairs
@@ -1425,10 +1507,11 @@ def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, 
     pairs = T * top
     act = workspace.get("moe_act", (pairs, ff), x.dtype)
     if not (use_fast_experts and x.dtype == torch.bfloat16 and fast_experts_supported(h, ff)):
-        moe_experts_plain(x, w_gate_up, w_down, experts, weights, act, y, weight_on_input, interleaved)
+        moe_experts_plain(x, w_gate_up, w_down, experts, weights, act, y, weight_on_input, interleaved, activation)
         return
     _need_cuda(x, w_gate_up, w_down, experts, weights, y)
-    assert tuple(w_gate_up.shape) == (E, 2 * ff, h) and w_gate_up.dtype == w_down.dtype == x.dtype and tuple(y.shape) == (T, h)
+    gated = activation == "swiglu"
+    assert tuple(w_gate_up.shape) == (E, (2 if gated else 1) * ff, h) and w_gate_up.dtype == w_down.dtype == x.dtype and tuple(y.shape) == (T, h)
     assert y.dtype == torch.float32 and experts.dtype == torch.int32 and weights.dtype == torch.float32
     ints = workspace.get("moe_ints", (E + 1 + 3 * pairs,), torch.int32)
     offsets, order, inv, token_sorted = ints[:E + 1], ints[E + 1:E + 1 + pairs], ints[E + 1 + pairs:E + 1 + 2 * pairs], ints[E + 1 + 2 * pairs:]
@@ -1441,17 +1524,23 @@ def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, 
     _cost(2 * pairs * h * size)
     _check(lib.mb_moe_gather(_ptr(x), _ptr(order), _ptr(weights), _ptr(xs), _ptr(token_sorted), _ptr(weight_sorted), _ptr(inv), _c_int(pairs),
                              _c_int(h), _c_int(top), _c_int(int(weight_on_input)), _stream()), "experts' inputs gathered")
-    dense = (interleaved and pairs >= EXPERTS_DENSE_FROM * E and use_tensor_cores and not torch.cuda.is_current_stream_capturing())
+    dense = ((interleaved or not gated) and pairs >= EXPERTS_DENSE_FROM * E and use_tensor_cores and not torch.cuda.is_current_stream_capturing())
     if dense:
         rows = workspace.get("moe_rows", (pairs, h), torch.float32)
         bounds = offsets.tolist()                       # the one wait on the host: how many pairs each expert got
         active = [e for e in range(E) if bounds[e + 1] > bounds[e]]
         # (while the stages of a step are being recorded everything stays on one stream, in launch order)
         lanes = min(EXPERT_STREAMS, len(active)) if launch_log is None else 1
+        def first_product(lo, hi, e):
+            if gated:
+                gemm_swiglu(xs[lo:hi], w_gate_up[e], act[lo:hi], workspace)
+            else:
+                gemm_act(xs[lo:hi], w_gate_up[e], act[lo:hi], "relu2")
+
         if lanes <= 1:
             for e in active:
                 lo, hi = bounds[e], bounds[e + 1]
-                gemm_swiglu(xs[lo:hi], w_gate_up[e], act[lo:hi], workspace)
+                first_product(lo, hi, e)
                 gemm(act[lo:hi], w_down[e], rows[lo:hi])
         else:
             global stream_k
@@ -1466,7 +1555,7 @@ def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, 
                     if i < lanes:
                         side[i].wait_event(ready)
                     with torch.cuda.stream(side[i % lanes]):
-                        gemm_swiglu(xs[lo:hi], w_gate_up[e], act[lo:hi], workspace)
+                        first_product(lo, hi, e)
                         gemm(act[lo:hi], w_down[e], rows[lo:hi])
             finally:
                 stream_k = keep
@@ -1478,9 +1567,10 @@ def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, 
         _check(lib.mb_moe_combine(_ptr(rows), _ptr(inv), _ptr(None if weight_on_input else weights), _ptr(y), _c_int(T), _c_int(h),
                                   _c_int(top), _stream()), "experts' outputs added")
         return
-    _cost(touched * 2 * ff * h * size + pairs * (h + ff) * size, 4.0 * pairs * ff * h)
+    _cost(touched * (2 if gated else 1) * ff * h * size + pairs * (h + ff) * size, (4.0 if gated else 2.0) * pairs * ff * h)
     _check(lib.mb_moe_grouped_gate_up(_ptr(xs), _ptr(w_gate_up), _ptr(offsets), _ptr(act), _c_int(pairs), _c_int(h), _c_int(ff), _c_int(E),
-                                      _c_int(int(interleaved)), _stream()), "experts, gate|up, SwiGLU (grouped, tensor cores)")
+                                      _c_int(int(interleaved)), _c_int(EXPERT_ACTIVATIONS[activation]), _stream()),
+           "experts, gate|up, SwiGLU (grouped, tensor cores)" if gated else "experts, up, relu squared (grouped, tensor cores)")
     scale = None if weight_on_input else weight_sorted
     _cost(touched * ff * h * size + pairs * ff * size + 2 * pairs * h * 4, 2.0 * pairs * ff * h)
     if top == 1:           # every pair has a row of y to itself: the product adds into it

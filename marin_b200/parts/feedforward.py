@@ -6,7 +6,7 @@ Interface: ``forward(x, ctx, residual)`` reads ``x`` ``[T, hidden]`` (activation
 """
 from __future__ import annotations
 
-from typing import Dict, List
+from typing import Dict, List, Optional
 
 import torch
 
@@ -109,31 +109,79 @@ class PolyNormMLP(FeedForward):
         return None
 
 
+@register_feedforward("act_mlp")
+class ActMLP(FeedForward):
+    """``down( act( x W_up^T ) )`` without a gate; ``activation`` "relu2": the square of relu, element by element."""
+
+    def __init__(self, hidden: int, intermediate: int, name: str, activation: str = "relu2", names=("up", "down")):
+        self.hidden, self.intermediate, self.name, self.activation = int(hidden), int(intermediate), name, activation
+        if activation not in ("relu2",):
+            raise ValueError(f"act_mlp: unknown activation {activation!r}")
+        self.up_name, self.down_name = (f"{name}.{n}" for n in names)
+        self.w_up = self.w_down = None
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        h, i = self.hidden, self.intermediate
+        return [TensorSpec(self.up_name, (i, h)), TensorSpec(self.down_name, (h, i))]
+
+    def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        self.w_up = rt.matrix(tensors.pop(self.up_name))
+        self.w_down = rt.matrix(tensors.pop(self.down_name))
+
+    def forward(self, x, ctx, residual: torch.Tensor):
+        T = x.shape[0]
+        act = ctx.workspace.get("ffn_act", (T, self.intermediate), x.dtype)
+        ops.stage_name = "up, activation"
+        ops.gemm_act(x, self.w_up, act, self.activation)
+        ops.stage_name = "down"
+        ops.gemm(act, self.w_down, residual, accumulate=True)
+        return None
+
+
 @register_feedforward("routed_experts")
 class RoutedExperts(FeedForward):
-    """A mixture of small SwiGLU feed-forwards of which every token uses ``top``: ``out = sum_e expert_e(.)`` over the chosen ones.
+    """A mixture of small feed-forwards of which every token uses ``top``: ``out = sum_e expert_e(.)`` over the chosen ones.
 
-    Router: ``z = h W_r^T`` in float32 (the matrix is kept in float32), scores ``sigmoid(z)`` (``score="sigmoid"``) or the
-    softmax of ``z`` over all experts; the ``top`` largest are chosen (the lower expert among equals) and their scores are
-    the weights, divided by their sum if ``renormalize``.  ``weight_on`` "input": the weight multiplies what the expert
-    reads, ``expert(w h)``, so it passes through the activation; "output": ``w expert(h)``.  Experts have no biases:
-    ``down( silu(gate x) * (up x) )``.  Nothing is read back to the host: routing, grouping and the experts' products
-    are kernels over device arrays, so single-token steps can be captured in graphs.
-    ``names``: the router's tensor and the pattern of an expert's tensors inside ``name`` (``{e}`` the expert's number)."""
+    Router (``router="learned"``): ``z = h W_r^T`` in float32 (the matrix is kept in float32), scores ``sigmoid(z)``
+    (``score="sigmoid"``) or the softmax of ``z`` over all experts; the ``top`` largest are chosen (the lower expert among
+    equals) and their scores are the weights, divided by their sum if ``renormalize``.  ``router="table"``: no scores at all;
+    an integer table ``[vocab, top]`` names the experts of every token id, each with the weight ``1 / top`` (the choice
+    depends on the token alone, not on the layer's input).  ``weight_on`` "input": the weight multiplies what the expert
+    reads, ``expert(w h)``, so it passes through the activation; "output": ``w expert(h)``.  Experts have no biases;
+    ``activation`` "swiglu": ``down( silu(gate x) * (up x) )``; "relu2": no gate, ``down( relu(up x)^2 )``.
+    ``shared_intermediate``: one more expert of that width (same form, tensors ``shared.*``) that every token uses with
+    weight 1.  Nothing is read back to the host: routing, grouping and the experts' products are kernels over device arrays,
+    so single-token steps can be captured in graphs.
+    ``names``: the router's (or table's) tensor and the pattern of an expert's tensors inside ``name`` (``{e}`` the expert's
+    number)."""
 
-    NAMES = {"router": "router.weight", "gate": "experts.{e}.gate_proj.weight", "up": "experts.{e}.up_proj.weight",
-             "down": "experts.{e}.down_proj.weight"}
+    NAMES = {"router": "router.weight", "table": "table", "gate": "experts.{e}.gate_proj.weight", "up": "experts.{e}.up_proj.weight",
+             "down": "experts.{e}.down_proj.weight", "shared_up": "shared.up", "shared_down": "shared.down"}
 
     def __init__(self, hidden: int, intermediate: int, experts: int, top: int, name: str, score: str = "sigmoid",
-                 renormalize: bool = False, weight_on: str = "input", names=None):
+                 renormalize: bool = False, weight_on: str = "input", names=None, router: str = "learned", vocab: int = 0,
+                 activation: str = "swiglu", shared_intermediate: Optional[int] = None):
         self.hidden, self.intermediate, self.experts, self.top, self.name = int(hidden), int(intermediate), int(experts), int(top), name
         if not 1 <= self.top <= self.experts:
             raise ValueError(f"routed_experts: top {top} of {experts} experts")
         if score not in ops.SCORE_MODES or weight_on not in ("input", "output"):
             raise ValueError(f"routed_experts: score {score!r} / weight_on {weight_on!r}")
+        if router not in ("learned", "table") or activation not in ops.EXPERT_ACTIVATIONS:
+            raise ValueError(f"routed_experts: router {router!r} / activation {activation!r}")
+        if router == "table" and int(vocab) <= 0:
+            raise ValueError("routed_experts: a table over the token ids needs the vocabulary's size")
         self.score, self.renormalize, self.weight_on = score, bool(renormalize), weight_on
+        self.routing, self.vocab, self.activation = router, int(vocab), activation
+        self.gated = activation == "swiglu"
         self.names = dict(self.NAMES, **(names or {}))
-        self.router = self.w_gate_up = self.w_down = None
+        self.router = self.table = self.w_gate_up = self.w_down = None
+        self.shared = None
+        if shared_intermediate:
+            if self.gated:
+                self.shared = SwiGLU(hidden, int(shared_intermediate), f"{name}.shared")
+            else:
+                self.shared = ActMLP(hidden, int(shared_intermediate), name, activation,
+                                     names=(self.names["shared_up"], self.names["shared_down"]))
 
     def _n(self, key: str, e: int = 0) -> str:
         return f"{self.name}.{self.names[key].format(e=e)}"
@@ -142,31 +190,58 @@ class RoutedExperts(FeedForward):
         h, i = self.hidden, self.intermediate
         specs = []
         for e in range(self.experts):
-            specs += [TensorSpec(self._n("gate", e), (i, h)), TensorSpec(self._n("up", e), (i, h)), TensorSpec(self._n("down", e), (h, i))]
-        return specs + [TensorSpec(self._n("router"), (self.experts, h), "bias")]
+            if self.gated:
+                specs.append(TensorSpec(self._n("gate", e), (i, h)))
+            specs += [TensorSpec(self._n("up", e), (i, h)), TensorSpec(self._n("down", e), (h, i))]
+        if self.routing == "table":
+            specs.append(TensorSpec(self._n("table"), (self.vocab, self.top), "int_table", limit=self.experts))
+        else:
+            specs.append(TensorSpec(self._n("router"), (self.experts, h), "bias"))
+        if self.shared is not None:
+            specs += self.shared.tensor_specs()
+        return specs
 
     def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
         # one tensor per kind for all experts: an expert's gate and up rows in one matrix, [E, 2 ff, h]; down [E, h, ff].  Where
         # the dense product's SwiGLU epilogue applies, the rows alternate in blocks of 16 as it reads them, so that an expert
-        # with many tokens can go to that product as it is; otherwise gate rows come first.
-        self.interleaved = ops.can_fuse_swiglu(rt.dtype, self.hidden, self.intermediate)
-        join = ops.interleave_gate_up if self.interleaved else (lambda g, u: torch.cat([g, u], dim=0))
-        self.w_gate_up = rt.matrix(torch.stack([join(tensors.pop(self._n("gate", e)), tensors.pop(self._n("up", e)))
-                                                for e in range(self.experts)]))
+        # with many tokens can go to that product as it is; otherwise gate rows come first.  Without a gate: up alone, [E, ff, h].
+        if self.gated:
+            self.interleaved = ops.can_fuse_swiglu(rt.dtype, self.hidden, self.intermediate)
+            join = ops.interleave_gate_up if self.interleaved else (lambda g, u: torch.cat([g, u], dim=0))
+            self.w_gate_up = rt.matrix(torch.stack([join(tensors.pop(self._n("gate", e)), tensors.pop(self._n("up", e)))
+                                                    for e in range(self.experts)]))
+        else:
+            self.interleaved = False
+            self.w_gate_up = rt.matrix(torch.stack([tensors.pop(self._n("up", e)) for e in range(self.experts)]))
         self.w_down = rt.matrix(torch.stack([tensors.pop(self._n("down", e)) for e in range(self.experts)]))
-        self.router = rt.f32(tensors.pop(self._n("router")))
+        if self.routing == "table":
+            table = tensors.pop(self._n("table")).to(torch.int32)
+            if int(table.min()) < 0 or int(table.max()) >= self.experts:
+                raise ValueError(f"{self._n('table')}: names experts outside 0..{self.experts - 1}")
+            self.table = table.to(rt.device).contiguous()
+        else:
+            self.router = rt.f32(tensors.pop(self._n("router")))
+        if self.shared is not None:
+            self.shared.load(tensors, rt)
         self.rt = rt
 
     def bytes_read(self, tokens: int, dtype) -> int:
         """Only the experts that some token chose are read: at most ``tokens * top`` of them."""
-        per_expert = 3 * self.hidden * self.intermediate * element_size(dtype)
-        return min(self.experts, tokens * self.top) * per_expert + self.experts * self.hidden * 4
+        per_expert = (3 if self.gated else 2) * self.hidden * self.intermediate * element_size(dtype)
+        routing = tokens * self.top * 4 if self.routing == "table" else self.experts * self.hidden * 4
+        shared = self.shared.bytes_read(tokens, dtype) if self.shared is not None else 0
+        return min(self.experts, tokens * self.top) * per_expert + routing + shared
 
     def flops(self, tokens: int, pairs: int = 0) -> float:
-        return 2.0 * tokens * self.hidden * (self.experts + 3 * self.top * self.intermediate)
+        routing = self.experts if self.routing == "learned" else 0
+        shared = self.shared.flops(tokens, pairs) if self.shared is not None else 0.0
+        return 2.0 * tokens * self.hidden * (routing + (3 if self.gated else 2) * self.top * self.intermediate) + shared
 
     def kernel_jobs(self, dtype) -> Dict[str, tuple]:
-        return ops.moe_jobs(dtype, self.hidden, self.intermediate)
+        jobs = ops.moe_jobs(dtype, self.hidden, self.intermediate)
+        if not self.gated:
+            jobs.update(ops.library_jobs("mb_activations"))
+        return jobs
 
     def forward(self, x, ctx, residual: torch.Tensor):
         T = x.shape[0]
@@ -174,7 +249,13 @@ class RoutedExperts(FeedForward):
         chosen = ws.get("moe_experts", (T, self.top), torch.int32)
         weights = ws.get("moe_weights", (T, self.top), torch.float32)
         ops.stage_name = "router"
-        ops.moe_route(x, self.router, chosen, weights, self.score, self.renormalize)
+        if self.routing == "table":
+            ops.moe_table_route(ctx.token_ids, self.table, self.experts, chosen, weights)
+        else:
+            ops.moe_route(x, self.router, chosen, weights, self.score, self.renormalize)
         ops.stage_name = "experts"
-        ops.moe_experts(x, self.w_gate_up, self.w_down, chosen, weights, residual, self.weight_on == "input", ws, self.interleaved)
+        ops.moe_experts(x, self.w_gate_up, self.w_down, chosen, weights, residual, self.weight_on == "input", ws, self.interleaved,
+                        self.activation)
+        if self.shared is not None:
+            self.shared.forward(x, ctx, residual)
         return None

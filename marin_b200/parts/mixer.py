@@ -36,6 +36,9 @@ class PagedKV:
     head_dim: int
     window: Optional[int] = None
     v_head_dim: Optional[int] = None
+    #: True: a position's values are the first ``v_head_dim`` elements of its key row (a latent that keys and values share);
+    #: no value pages are kept, and the mixer's view hands the key pages out as values too
+    values_in_keys: bool = False
 
     @property
     def value_dim(self) -> int:
@@ -43,7 +46,7 @@ class PagedKV:
 
     def bytes_per_token(self, dtype: torch.dtype) -> int:
         """Bytes one position of one layer holds in the cache (keys and values)."""
-        return self.kv_heads * (self.head_dim + self.value_dim) * element_size(dtype)
+        return self.kv_heads * (self.head_dim + (0 if self.values_in_keys else self.value_dim)) * element_size(dtype)
 
     def bytes_read(self, context: int, dtype: torch.dtype) -> int:
         """Bytes one decoded token reads of a sequence of ``context`` positions."""
@@ -320,7 +323,8 @@ class SinkAttention(Mixer):
     business).  Score ``q . k * scale``.  A position sees the keys before it and itself; ``window`` keeps the last so
     many, ``chunk`` keeps those of its own chunk (``floor(i / chunk) = floor(j / chunk)``, counted from the sequence's
     first position wherever a prompt was cut).  ``sink``: the softmax has one more term in its denominator, a key of
-    score 0 without a value: ``p_j = exp(s_j) / (1 + sum_j exp(s_j))``.
+    score 0 without a value: ``p_j = exp(s_j) / (1 + sum_j exp(s_j))``; ``sink="learned"``: the term is ``exp(b_h)`` with a
+    learned number ``b_h`` per query head (tensor ``sink`` ``[heads]``, not scaled).
 
     ``value_mix``: None, or a name that ties layers together: the first layer of that name in the model leaves its values
     (of the step's tokens) where the later ones find them, and those cache ``(1 - lam) v + lam v_first`` with their own
@@ -331,7 +335,7 @@ class SinkAttention(Mixer):
 
     NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight", "g": "g_proj.weight",
              "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias",
-             "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "lam": "value_mix"}
+             "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "lam": "value_mix", "sink": "sink"}
 
     def __init__(self, hidden: int, heads: int, kv_heads: int, head_dim: int, name: str, position: PartSpec,
                  v_head_dim: Optional[int] = None, scale: Optional[float] = None, bias: bool = False, qk_norm: Optional[str] = "head",
@@ -348,6 +352,8 @@ class SinkAttention(Mixer):
         self.window = int(window) if window else None
         self.chunk = int(chunk) if chunk else None
         self.sink, self.gate = bool(sink), bool(gate)
+        self.learned_sink = sink == "learned"
+        self.sink_logits = None
         self.value_mix, self.first_of_mix = value_mix, bool(first_of_mix)
         self.position = lookup("position", position.kind)(**position.params)
         self.names = dict(self.NAMES, **(names or {}))
@@ -378,6 +384,8 @@ class SinkAttention(Mixer):
                       TensorSpec(self._n("k_norm"), (self.head_dim if n else self.k_dim,), "norm")]
         if self.value_mix is not None:
             specs.append(TensorSpec(self._n("lam"), (), "bias", 0.5))
+        if self.learned_sink:
+            specs.append(TensorSpec(self._n("sink"), (self.heads,), "bias"))
         return specs
 
     def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
@@ -393,6 +401,8 @@ class SinkAttention(Mixer):
             self.k_weight = rt.f32(tensors.pop(self._n("k_norm")))
         if self.value_mix is not None:
             self.lam = rt.f32(tensors.pop(self._n("lam"))).reshape(1)
+        if self.learned_sink:
+            self.sink_logits = rt.f32(tensors.pop(self._n("sink")))
         self.position.load(tensors, rt)
         self.rt = rt
 
@@ -430,14 +440,129 @@ class SinkAttention(Mixer):
         pos = self.position
         ops.qkv_finish(rows, q, self.q_b, self.k_b, self.v_b, self.qk_norm, self.q_weight, self.k_weight, self.norm_eps, ctx.positions,
                        pos.inv_freq, pos.rotary_dim, pos.magnitude, cache.slot_mapping, cache.k, cache.v, mode, shared, self.lam,
-                       self.heads, self.kv_heads, self.head_dim, self.v_head_dim, writes)
+                       self.heads, self.kv_heads, self.head_dim, self.v_head_dim, writes, pos.interleaved)
         out = ws.get("attn_out", (T, self.o_dim), x.dtype)
         ops.stage_name = "attention"
         gate = rows[:, self.q_dim + self.k_dim + self.v_dim:] if self.gate else None
         plans = ctx.decode_plans
         ops.attention_sink(q, cache.k, cache.v, out, ctx, cache.block_table, self.heads, self.kv_heads, self.head_dim, self.v_head_dim,
                            self.scale, self.window or 0, self.chunk or 0, self.sink, gate,
-                           plans.get(self.decode_plan_key()) if plans else None)
+                           plans.get(self.decode_plan_key()) if plans else None, self.sink_logits)
+        ops.stage_name = "o"
+        ops.gemm(out, self.w_o, residual, accumulate=True)
+        return None
+
+
+@register_mixer("latent_attention")
+class LatentAttention(Mixer):
+    """Causal softmax attention whose keys and values are expanded per head from one latent row per position
+    (multi-head latent attention: DeepSeek-AI, "DeepSeek-V2: A Strong, Economical, and Efficient Mixture-of-Experts
+    Language Model").
+
+    ``q = W_q h``, per head ``head_dim`` unrotated and ``rot_dim`` rotated numbers.  ``W_dkv h`` gives ``kv_rank`` numbers
+    that, divided by their root mean square times a weight, are the latent ``c``, and ``rot_dim`` numbers that, rotated, are a
+    key part ``k_r`` shared by all heads; the page row of a position is ``[c | k_r]``, nothing else is cached.  Head ``a`` has
+    the key ``[W_uk_a c | k_r]`` and the value ``W_uv_a c``; the score is their product with ``[q_a | rotated q_a]`` times
+    ``scale``; the softmax may have a sink as in :class:`SinkAttention`.  Computed in the absorbed form: the queries are taken
+    into the latent's space, ``q'_a = [W_uk_a^T q_a | rotated q_a]``, every head then reads the same page rows (one kv head
+    whose values are the rows' first ``kv_rank`` elements), and the heads' sums of latents are expanded once per token,
+    ``W_uv_a (sum_j p_j c_j)``.  A run that reads another run's cache (``cache_of``) has no ``W_dkv`` of its own in use: it
+    computes its queries, reads the owner's rows and applies its own ``W_uk``, ``W_uv``, sink and ``W_o``; ``own_latent=False``
+    says the layer brings no ``dkv`` tensors at all.
+    """
+
+    NAMES = {"q": "q", "dkv": "dkv", "c_norm": "dkv.norm", "uk": "uk", "uv": "uv", "o": "o", "sink": "sink"}
+
+    def __init__(self, hidden: int, heads: int, head_dim: int, rot_dim: int, v_head_dim: int, kv_rank: int, name: str, position: PartSpec,
+                 scale: Optional[float] = None, norm_eps: float = 1e-6, sink=False, own_latent: bool = True, names=None):
+        self.hidden, self.heads, self.head_dim, self.rot_dim = int(hidden), int(heads), int(head_dim), int(rot_dim)
+        self.v_head_dim, self.kv_rank = int(v_head_dim), int(kv_rank)
+        self.name, self.norm_eps = name, float(norm_eps)
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.head_dim + self.rot_dim)
+        self.sink, self.learned_sink = bool(sink), sink == "learned"
+        self.own_latent = bool(own_latent)
+        self.position = lookup("position", position.kind)(**position.params)
+        if self.position.rotary_dim > self.rot_dim:
+            raise ValueError(f"latent_attention: {self.position.rotary_dim} rotated dimensions in a rotated part of {self.rot_dim}")
+        self.names = dict(self.NAMES, **(names or {}))
+        self.q_head = self.head_dim + self.rot_dim
+        self.q_dim, self.row_dim = self.heads * self.q_head, self.kv_rank + self.rot_dim
+        self.o_dim = self.heads * self.v_head_dim
+        self.w_in = self.w_uk_t = self.w_uv = self.w_o = self.c_weight = self.sink_logits = None
+
+    def _n(self, key: str) -> str:
+        return f"{self.name}.{self.names[key]}"
+
+    def cache_need(self):
+        return PagedKV(1, self.row_dim, None, self.kv_rank, values_in_keys=True)
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        h, r = self.hidden, self.kv_rank
+        specs = [TensorSpec(self._n("q"), (self.q_dim, h))]
+        if self.own_latent:
+            specs += [TensorSpec(self._n("dkv"), (self.row_dim, h)), TensorSpec(self._n("c_norm"), (r,), "norm")]
+        specs += [TensorSpec(self._n("uk"), (self.heads * self.head_dim, r)), TensorSpec(self._n("uv"), (self.o_dim, r)),
+                  TensorSpec(self._n("o"), (h, self.o_dim))]
+        if self.learned_sink:
+            specs.append(TensorSpec(self._n("sink"), (self.heads,), "bias"))
+        return specs
+
+    def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        parts = [tensors.pop(self._n("q"))]
+        if self.own_latent:
+            parts.append(tensors.pop(self._n("dkv")))
+            self.c_weight = rt.f32(tensors.pop(self._n("c_norm")))
+        self.w_in = rt.matrix(torch.cat(parts, dim=0))
+        # per head the key expansion transposed, [heads, kv_rank, head_dim]: the queries are multiplied into the latent's space
+        uk = tensors.pop(self._n("uk")).reshape(self.heads, self.head_dim, self.kv_rank)
+        self.w_uk_t = rt.matrix(uk.transpose(1, 2))
+        self.w_uv = rt.matrix(tensors.pop(self._n("uv")).reshape(self.heads, self.v_head_dim, self.kv_rank))
+        self.w_o = rt.matrix(tensors.pop(self._n("o")))
+        if self.learned_sink:
+            self.sink_logits = rt.f32(tensors.pop(self._n("sink")))
+        self.position.load(tensors, rt)
+        self.rt = rt
+
+    def flops(self, tokens: int, pairs: int = 0) -> float:
+        return super().flops(tokens, pairs) + 2.0 * pairs * self.heads * (self.row_dim + self.kv_rank)
+
+    def kernel_jobs(self, dtype) -> Dict[str, tuple]:
+        jobs = ops.library_jobs("mb_attention_latent")
+        jobs.update(ops.sink_attention_jobs(dtype, self.heads, 1, self.row_dim, self.kv_rank, values_in_keys=True))
+        return jobs
+
+    def decode_plan_key(self):
+        return ("latent_attention", self.heads, self.row_dim, self.kv_rank)
+
+    def decode_plan(self, requests: int, span: int, rt: Runtime):
+        return ops.sink_decode_plan(rt.dtype, requests, self.heads, 1, self.row_dim, self.kv_rank, span, 0, 0, values_in_keys=True)
+
+    def forward(self, x, ctx, cache, residual: torch.Tensor):
+        T = x.shape[0]
+        ws = ctx.workspace
+        writes = cache.owner
+        if writes and not self.own_latent:
+            raise ValueError("latent_attention: a layer without a latent of its own must read another run's cache")
+        H, dn, dr, r, D = self.heads, self.head_dim, self.rot_dim, self.kv_rank, self.row_dim
+        w = self.w_in if writes else self.w_in[: self.q_dim]
+        ops.stage_name = "q|dkv"
+        rows = ws.get("q_dkv", (T, w.shape[0]), x.dtype)
+        ops.gemm(x, w, rows)
+        ops.stage_name = "heads"
+        q = ws.get("q_latent", (T, H * D), x.dtype)
+        pos = self.position
+        ops.latent_finish(rows, q, self.c_weight, self.norm_eps, ctx.positions, pos.inv_freq, pos.rotary_dim, pos.interleaved,
+                          cache.slot_mapping, cache.k, H, dn, dr, r, writes)
+        ops.stage_name = "queries into the latent"
+        ops.heads_product(rows, self.q_head, dn, self.w_uk_t, q, D)
+        mixed = ws.get("latent_out", (T, H * r), x.dtype)
+        ops.stage_name = "attention"
+        plans = ctx.decode_plans
+        ops.attention_sink(q, cache.k, cache.k, mixed, ctx, cache.block_table, H, 1, D, r, self.scale, 0, 0, self.sink, None,
+                           plans.get(self.decode_plan_key()) if plans else None, self.sink_logits)
+        ops.stage_name = "values from the latent"
+        out = ws.get("attn_out", (T, self.o_dim), x.dtype)
+        ops.heads_product(mixed, r, r, self.w_uv, out, self.v_head_dim)
         ops.stage_name = "o"
         ops.gemm(out, self.w_o, residual, accumulate=True)
         return None

@@ -87,6 +87,39 @@ class RescaledRotary(Rotary):
         self.inv_freq = torch.tensor(self.frequencies(), dtype=torch.float64).to(torch.float32).to(rt.device)
 
 
+@register_position("rope_llama3")
+class BandScaledRotary(Rotary):
+    """Rotary embedding whose slow pairs are slowed further for contexts longer than the ``original`` one, by wavelength
+    bands (the frequency scaling of Llama 3.1).  With ``f_i = theta^(-2i/d)`` and wavelength ``l_i = 2 pi / f_i``: pairs with
+    ``l_i < original / high`` keep ``f_i``; pairs with ``l_i > original / low`` turn at ``f_i / factor``; between the two, with
+    ``s = (original / l_i - low) / (high - low)``, at ``(1 - s) f_i / factor + s f_i``.  Sines and cosines keep their size.
+    The table is made in float64 on the host and rounded once to float32; angles are float32 products of it."""
+
+    def __init__(self, head_dim: int, theta: float, factor: float, low: float, high: float, original: float,
+                 rotary_dim: Optional[int] = None, interleaved: bool = False):
+        super().__init__(head_dim, theta, rotary_dim, interleaved)
+        self.factor, self.low, self.high, self.original = float(factor), float(low), float(high), float(original)
+        if self.factor <= 0 or self.original <= 0 or self.low <= 0 or self.high <= self.low:
+            raise ValueError("rope_llama3: factor, original and low must be positive and high above low")
+
+    def frequencies(self):
+        """The angle per position of every pair, as Python floats (float64)."""
+        out = []
+        for i in range(self.rotary_dim // 2):
+            f = self.theta ** (-2.0 * i / self.rotary_dim)
+            wavelength = 2.0 * math.pi / f
+            if wavelength > self.original / self.low:
+                f = f / self.factor
+            elif wavelength >= self.original / self.high:
+                s = (self.original / wavelength - self.low) / (self.high - self.low)
+                f = (1.0 - s) * f / self.factor + s * f
+            out.append(f)
+        return out
+
+    def load(self, tensors, rt: Runtime) -> None:
+        self.inv_freq = torch.tensor(self.frequencies(), dtype=torch.float64).to(torch.float32).to(rt.device)
+
+
 @register_position("none")
 class NoPosition(PositionEncoding):
     def __init__(self, **_ignored):

@@ -19,13 +19,15 @@ class TensorSpec:
     N(0, 0.02)), ``norm`` (kept f32 on the device, 1 + N(0, 0.05)), ``bias`` (kept f32 on
     the device, N(0, 0.02): offsets, mixing coefficients, small tables added to scores),
     ``table`` (an embedding table, treated like a matrix), ``int_table`` (int32).  ``mean`` moves the centre of the random
-    initialisation (a mixing coefficient that should start near 1 or near 1/n rather than near 0).
+    initialisation (a mixing coefficient that should start near 1 or near 1/n rather than near 0).  ``limit`` (integer
+    tables): entries are drawn below it, those of a row all different (a table that names a token's experts).
     """
 
     name: str
     shape: Tuple[int, ...]
     role: str = "matrix"
     mean: Optional[float] = None
+    limit: Optional[int] = None
 
 
 @dataclass

@@ -35,6 +35,11 @@ def random_tensor(spec: TensorSpec, seed: int, dtype: torch.dtype, device="cpu",
                   matrix_std: float = MATRIX_STD, norm_std: float = NORM_STD) -> torch.Tensor:
     gen = torch.Generator(device=device)
     gen.manual_seed(_seed_for(seed, spec.name))
+    if spec.role == "int_table" and spec.limit:
+        # every row a random choice of different numbers below the limit
+        rows, cols = int(spec.shape[0]), int(spec.shape[1])
+        draws = torch.rand((rows, int(spec.limit)), generator=gen, device=device)
+        return draws.argsort(dim=1)[:, :cols].to(torch.int32).contiguous()
     if spec.role == "int_table":
         return torch.randint(0, 2 ** 15, spec.shape, generator=gen, device=device, dtype=torch.int32)
     count = 1
