@@ -2,13 +2,16 @@
 // tensor cores (mma.sync), compiled for one head layout:
 //   -DHEAD_DIM (keys and queries), -DV_DIM (values), -DGROUP (query heads per kv head); both sizes multiples of 16 up to 128.
 // A position i sees the keys j <= i with j >= lo(i) = max(i - window + 1 (window > 0), floor(i / chunk) chunk (chunk > 0), 0).
-//   p_j = exp(s_j) / (sink + sum_j exp(s_j)), s_j = q_i . k_j * scale, sink = 1 (a key of score 0 without a value) or 0;
+//   p_j = exp(s_j) / (sink + sum_j exp(s_j)), s_j = q_i . k_j * scale, sink = exp(b_h) (a key without a value whose score b_h is
+//   0 or a learned number per query head, not scaled) or 0;
 //   out_i = (sum_j p_j v_j) * sigmoid(gate_i) where a gate is given.
 // Scores, maxima and sums are float32 (in the exp2 domain); the weights are rounded to bf16 for the product with V.
 // Prompt portions: 64 queries x 64-key blocks per CTA, only the blocks between lo(first query) and the last query.
 // Single tokens: the visible keys of a sequence split over CTAs, partial (max, sum, accumulator) merged by a second kernel
 // in chunk order, which also adds the sink and applies the gate.
 // K pages [page][kv_head][offset][HEAD_DIM], V pages [page][kv_head][offset][V_DIM].
+// -DV_IN_K: there are no value pages; a position's values are the first V_DIM elements of its key row (a latent that keys and
+// values share), so a key block in shared memory serves both products and nothing is fetched twice.
 #define MB_LIB "attention_sink_fast"
 #define MB_LIB_ID 15
 #include "common.cuh"
@@ -24,14 +27,21 @@
 #ifndef GROUP
 #define GROUP 4
 #endif
-static_assert(HEAD_DIM % 16 == 0 && HEAD_DIM >= 16 && HEAD_DIM <= 128, "key heads: a multiple of 16 up to 128");
+static_assert(HEAD_DIM % 16 == 0 && HEAD_DIM >= 16 && HEAD_DIM <= 256, "key heads: a multiple of 16 up to 256");
 static_assert(V_DIM % 16 == 0 && V_DIM >= 16 && V_DIM <= 128, "value heads: a multiple of 16 up to 128");
 static_assert(GROUP >= 1 && GROUP <= 8, "1 to 8 query heads per kv head");
 
 #define D HEAD_DIM
 #define DV V_DIM
 #define LDK (D + 8)                   // padded rows in shared memory (elements): ldmatrix without bank conflicts
+#ifdef V_IN_K
+static_assert(V_DIM <= HEAD_DIM, "values inside the key rows cannot be wider than the rows");
+#define LDV LDK
+#define V_ROWS 0                      // rows of shared memory a value block takes beside its key block
+#else
 #define LDV (DV + 8)
+#define V_ROWS BN
+#endif
 #define BM 64
 #define BN 64
 #define LOG2E 1.4426950408889634f
@@ -52,7 +62,11 @@ __device__ __forceinline__ int first_seen(int pos, int window, int chunk) {
 // The rows of one 64-key block of K and V (cp.async); keys outside [k_first, k_last] are zero (their pages may not exist).
 __device__ __forceinline__ void load_kv_block(bf16* dst_k, bf16* dst_v, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                                               const int* __restrict__ table, int K, int kh, int page_shift, int key0, int k_first, int k_last) {
+#ifdef V_IN_K
+    constexpr int CK = D / 8, CV = 0;
+#else
     constexpr int CK = D / 8, CV = DV / 8;
+#endif
     const int page_mask = (1 << page_shift) - 1;
     for (int idx = threadIdx.x; idx < BN * (CK + CV); idx += 128) {
         const int row = idx / (CK + CV), c = idx % (CK + CV);
@@ -68,18 +82,23 @@ __device__ __forceinline__ void load_kv_block(bf16* dst_k, bf16* dst_v, const bf
     }
 }
 
-#define PF_SMEM ((BM * LDK + BN * LDK + BN * LDV) * 2)
+#define PF_SMEM ((BM * LDK + BN * LDK + V_ROWS * LDV) * 2)
 
 __global__ void __launch_bounds__(128, 2) attn_sink_prefill_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache, bf16* __restrict__ out,
     const int* __restrict__ block_table, int max_pages, const int* __restrict__ cu_tokens, const int* __restrict__ seq_lens,
-    int first_req, int K, int page_shift, float scale, int window, int chunk, int sink, const bf16* __restrict__ gate, int gate_stride) {
+    int first_req, int K, int page_shift, float scale, int window, int chunk, int sink, const float* __restrict__ sink_logit,
+    const bf16* __restrict__ gate, int gate_stride) {
     PDL_ENTER_EARLY();
     q = pdl_fresh(q); k_cache = pdl_fresh(k_cache); v_cache = pdl_fresh(v_cache); gate = pdl_fresh(gate);
     extern __shared__ __align__(16) uint8_t smem_raw[];
     bf16* sQ = reinterpret_cast<bf16*>(smem_raw);
     bf16* sK = sQ + BM * LDK;
+#ifdef V_IN_K
+    bf16* sV = sK;
+#else
     bf16* sV = sK + BN * LDK;
+#endif
     const int H = K * GROUP;
     const int r = first_req + blockIdx.z, h = blockIdx.y, qt = gridDim.x - 1 - blockIdx.x;   // long tiles first
     const int tok0 = cu_tokens[r], n = cu_tokens[r + 1] - tok0;
@@ -113,9 +132,10 @@ __global__ void __launch_bounds__(128, 2) attn_sink_prefill_kernel(
     const int qp[2] = {q_first + row0, q_first + row0 + 8};
     const int lo[2] = {first_seen(qp[0], window, chunk), first_seen(qp[1], window, chunk)};
     const float sl2 = scale * LOG2E;
-    // running maximum (log2 units) and this thread's share of the running sum, per row; the sink is a score of 0 and a 1 in the sum
+    // running maximum (log2 units) and this thread's share of the running sum, per row; the sink is a score (0 or the head's
+    // learned number, not scaled) and a 1 in the sum
     float m_run[2], l_run[2];
-    m_run[0] = m_run[1] = sink ? 0.0f : -INFINITY;
+    m_run[0] = m_run[1] = sink ? (sink_logit != nullptr ? sink_logit[h] * LOG2E : 0.0f) : -INFINITY;
     l_run[0] = l_run[1] = (sink && (lane & 3) == 0) ? 1.0f : 0.0f;
 
     for (int kb = kb_first; kb <= kb_last; ++kb) {
@@ -229,8 +249,8 @@ __global__ void __launch_bounds__(128, 2) attn_sink_prefill_kernel(
 // GROUP query heads of the kv head are rows 0..GROUP-1 of a 16-row tile; warp w takes keys 16 w .. 16 w + 15 of every block
 // with a running (max, sum) of its own.  The four warps are merged in shared memory in warp order and written as the chunk's
 // part: acc[chunk][request][head][DV] and ml[chunk][request][head][2] (max in log2 units, sum), float32.
-#define DEC_SMEM ((16 * LDK + BN * LDK + BN * LDV) * 2)
-static_assert(4 * GROUP * DV * 4 <= BN * LDK * 2 + BN * LDV * 2, "the warps' sums are written over the key and value block");
+#define DEC_SMEM ((16 * LDK + BN * LDK + V_ROWS * LDV) * 2)
+static_assert(4 * GROUP * DV * 4 <= BN * LDK * 2 + V_ROWS * LDV * 2, "the warps' sums are written over the key and value block");
 
 __global__ void __launch_bounds__(128) attn_sink_decode_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache, float* __restrict__ part_acc,
@@ -242,7 +262,11 @@ __global__ void __launch_bounds__(128) attn_sink_decode_kernel(
     __shared__ float s_m[4][8], s_l[4][8];
     bf16* sQ = reinterpret_cast<bf16*>(smem_raw);
     bf16* sK = sQ + 16 * LDK;
+#ifdef V_IN_K
+    bf16* sV = sK;
+#else
     bf16* sV = sK + BN * LDK;
+#endif
     const int chunk = blockIdx.x, kh = blockIdx.y, r = blockIdx.z, R = gridDim.z;
     const int H = K * GROUP;
     const int len = seq_lens[r], pos = len - 1;
@@ -355,13 +379,14 @@ __global__ void __launch_bounds__(128) attn_sink_decode_kernel(
     }
 }
 
-// out[r][h][:] = (sum_c acc_c 2^(m_c - M)) / (sink 2^(-M) + sum_c l_c 2^(m_c - M)) * sigmoid(gate), chunks in increasing order.
+// out[r][h][:] = (sum_c acc_c 2^(m_c - M)) / (sink 2^(b_h - M) + sum_c l_c 2^(m_c - M)) * sigmoid(gate), chunks in increasing order.
 // A block per (request, head): the chunks' weights 2^(m_c - M) are made side by side, then every output is one sum over the chunks.
 #define MG_THREADS 128
 #define MG_MAX_CHUNKS 1024
 __global__ void __launch_bounds__(MG_THREADS) attn_sink_merge_kernel(
     const float* __restrict__ part_acc, const float* __restrict__ part_ml, const int* __restrict__ seq_lens, int split, int window,
-    int chunk_size, int sink, int R, int H, const bf16* __restrict__ gate, int gate_stride, bf16* __restrict__ out) {
+    int chunk_size, int sink, const float* __restrict__ sink_logit, int R, int H, const bf16* __restrict__ gate, int gate_stride,
+    bf16* __restrict__ out) {
     PDL_ENTER();
     part_acc = pdl_fresh(part_acc); part_ml = pdl_fresh(part_ml); gate = pdl_fresh(gate);
     __shared__ float wgt[MG_MAX_CHUNKS], scratch[32];
@@ -371,7 +396,8 @@ __global__ void __launch_bounds__(MG_THREADS) attn_sink_merge_kernel(
     const int pos = len - 1;
     const int start = (first_seen(pos, window, chunk_size) / BN) * BN;
     const int chunks = min((len - start + split - 1) / split, MG_MAX_CHUNKS);
-    float mx = sink ? 0.0f : -INFINITY;
+    const float s0 = sink_logit != nullptr ? sink_logit[h] * LOG2E : 0.0f;        // the sink's score in log2 units
+    float mx = sink ? s0 : -INFINITY;
     for (int c = threadIdx.x; c < chunks; c += MG_THREADS) {
         const float mc = part_ml[(((size_t)c * R + r) * H + h) * 2];
         wgt[c] = mc;
@@ -385,7 +411,7 @@ __global__ void __launch_bounds__(MG_THREADS) attn_sink_merge_kernel(
         wgt[c] = f;
         part = fmaf(part_ml[(((size_t)c * R + r) * H + h) * 2 + 1], f, part);
     }
-    const float total = block_sum(part, scratch) + (sink ? exp2f(-M) : 0.0f);       // (its barriers publish wgt)
+    const float total = block_sum(part, scratch) + (sink ? exp2f(s0 - M) : 0.0f);       // (its barriers publish wgt)
     const float inv = 1.0f / total;
     for (int i = threadIdx.x; i < DV; i += MG_THREADS) {
         float a = 0.0f;
@@ -428,11 +454,11 @@ MB_API int mb_attn_sink_decode(const void* q, const void* k_cache, const void* v
 
 // The parts of every request merged in chunk order, with the sink and the gate: out bf16 [requests][K * GROUP][V_DIM].
 MB_API int mb_attn_sink_merge(const float* part_acc, const float* part_ml, void* out, const int* seq_lens, int requests, int K, int window,
-                              int chunk, int sink, const void* gate, int gate_stride, int split, cudaStream_t s) {
+                              int chunk, int sink, const void* gate, int gate_stride, int split, const float* sink_logit, cudaStream_t s) {
     if (requests <= 0) return 0;
     if (split <= 0) return MB_ERR_BAD_SIZE;
     return launch_kernel(attn_sink_merge_kernel, requests * K * GROUP, MG_THREADS, 0, s, 0, (const float*)part_acc,
-                         (const float*)part_ml, seq_lens, split, window, chunk, sink, requests, K * GROUP, (const bf16*)gate, gate_stride,
+                         (const float*)part_ml, seq_lens, split, window, chunk, sink, sink_logit, requests, K * GROUP, (const bf16*)gate, gate_stride,
                          (bf16*)out);
 }
 
@@ -440,13 +466,13 @@ MB_API int mb_attn_sink_merge(const float* part_acc, const float* part_ml, void*
 MB_API int mb_attn_sink_prefill(const void* q, const void* k_cache, const void* v_cache, void* out, const int* block_table,
                                 int max_pages, const int* cu_tokens, const int* seq_lens, int first_req, int count, int max_query_len,
                                 int K, int page_size, float scale, int window, int chunk, int sink, const void* gate, int gate_stride,
-                                cudaStream_t s) {
+                                const float* sink_logit, cudaStream_t s) {
     if (count <= 0 || max_query_len <= 0) return 0;
     const int shift = page_shift_of(page_size);
     if (shift < 0 || window < 0 || chunk < 0) return MB_ERR_BAD_SIZE;
     cudaFuncSetAttribute(attn_sink_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM);
     dim3 grid((max_query_len + BM - 1) / BM, K * GROUP, count);
     return launch_kernel(attn_sink_prefill_kernel, grid, 128, PF_SMEM, s, 0, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
-                         (bf16*)out, block_table, max_pages, cu_tokens, seq_lens, first_req, K, shift, scale, window, chunk, sink,
+                         (bf16*)out, block_table, max_pages, cu_tokens, seq_lens, first_req, K, shift, scale, window, chunk, sink, sink_logit,
                          (const bf16*)gate, gate_stride);
 }

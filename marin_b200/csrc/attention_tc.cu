@@ -198,7 +198,7 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
     bf16* __restrict__ out, const int* __restrict__ block_table, int max_pages, const int* __restrict__ cu_tokens,
     const int* __restrict__ seq_lens, int first_req, int K, int page_shift, float scale, int window, int* __restrict__ error_flag,
-    int box_rows, int chunk, int sink, const bf16* __restrict__ gate, int gate_stride) {
+    int box_rows, int chunk, int sink, const float* __restrict__ sink_logit, const bf16* __restrict__ gate, int gate_stride) {
     extern __shared__ __align__(1024) uint8_t smem[];     // the swizzled tiles need 1024-byte alignment (checked below)
     uint8_t* sQ = smem;
     uint8_t* sKV = sQ + TA_Q_BYTES;                       // [buffer][K then V][half][64 rows][128 B]
@@ -393,9 +393,9 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_tc_kernel(
         const int lo_t = first_seen(qp, window, chunk);
         const float sl2 = scale * 1.4426950408889634f;
         const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
-        // the maximum O and l are currently scaled by (log2 units); a sink is a key of score 0 without a value: the maximum
-        // starts at 0 and the sum at 1
-        float m_used = sink ? 0.0f : -INFINITY, l_run = sink ? 1.0f : 0.0f;
+        // the maximum O and l are currently scaled by (log2 units); a sink is a key without a value whose score is 0 or the
+        // head's learned number (not scaled): the maximum starts there and the sum at 1
+        float m_used = sink ? (sink_logit != nullptr ? sink_logit[h] * 1.4426950408889634f : 0.0f) : -INFINITY, l_run = sink ? 1.0f : 0.0f;
         bool ok = true;
         long long r_s = 0, r_o = 0;
         const long long r_start = TA_T();
@@ -547,7 +547,8 @@ static int map_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t co
 MB_API int mb_attn_prefill_tc(const void* q, const void* k_cache, const void* v_cache, void* out, const int* block_table,
                               int max_pages, const int* cu_tokens, const int* seq_lens, int first_req, int requests,
                               int max_query_len, int tokens, int K, int page_size, long long cache_pages, float scale,
-                              int window, int* error_flag, int chunk, int sink, const void* gate, int gate_stride, cudaStream_t s) {
+                              int window, int* error_flag, int chunk, int sink, const void* gate, int gate_stride, const float* sink_logit,
+                              cudaStream_t s) {
     if (requests <= 0 || max_query_len <= 0) return 0;
     if (chunk < 0 || (gate != nullptr && (((uintptr_t)gate & 15) || gate_stride % 8 != 0))) return MB_ERR_BAD_SIZE;
     int page_shift = -1;
@@ -572,5 +573,5 @@ MB_API int mb_attn_prefill_tc(const void* q, const void* k_cache, const void* v_
     if (rc) return rc;
     dim3 grid((max_query_len + TA_BM - 1) / TA_BM, K * GROUP, requests);
     return launch_kernel(attn_prefill_tc_kernel, grid, 256, TA_SMEM, s, 0, mq, mk, mv, (bf16*)out, block_table, max_pages, cu_tokens,
-                         seq_lens, first_req, K, page_shift, scale, window, error_flag, box_rows, chunk, sink, (const bf16*)gate, gate_stride);
+                         seq_lens, first_req, K, page_shift, scale, window, error_flag, box_rows, chunk, sink, sink_logit, (const bf16*)gate, gate_stride);
 }

@@ -688,7 +688,7 @@ def attention(q, k_cache, v_cache, out, ctx, block_table, H, K, d, scale, window
                                          _ptr(ctx.cu_tokens), _ptr(ctx.seq_lens), _c_int(nd), _c_int(ctx.num_requests - nd),
                                          _c_int(ctx.max_query_len), _c_int(T), _c_int(K), _c_int(page_size),
                                          ctypes.c_longlong(k_cache.shape[0]), _c_float(scale), _c_int(window),
-                                         _ptr(_scratch_for(q.device).error), _c_int(0), _c_int(0), _ptr(None), _c_int(0), _stream()),
+                                         _ptr(_scratch_for(q.device).error), _c_int(0), _c_int(0), _ptr(None), _c_int(0), _ptr(None), _stream()),
                    "attention (prefill, tensor cores)")
         elif ctx.num_requests > nd:
             _attention_cost(q, T - nd, H, K, d, "prefill")
@@ -1243,14 +1243,13 @@ def attention_sink(q, k_cache, v_cache, out, ctx, block_table, H: int, K: int, d
         return
     size = q.element_size()
     per_row = H * (d + (3 if gate is not None else 2) * dv) * size
-    if (use_fast_sink_attention and fast_sink_attention_supported(q.dtype, H, K, d, dv) and page_size & (page_size - 1) == 0
-            and not values_in_keys and sink_logits is None):
-        lib = _sink_lib(d, dv, H // K)
+    if use_fast_sink_attention and fast_sink_attention_supported(q.dtype, H, K, d, dv, values_in_keys) and page_size & (page_size - 1) == 0:
+        lib = _sink_lib(d, dv, H // K, values_in_keys)
         max_pages = block_table.shape[1]
         nd = ctx.num_decode
         if nd > 0:
             if plan is None:
-                plan = sink_decode_plan(q.dtype, nd, H, K, d, dv, ctx.max_seq_len, window, chunk)
+                plan = sink_decode_plan(q.dtype, nd, H, K, d, dv, ctx.max_seq_len, window, chunk, values_in_keys)
             acc = ctx.workspace.get("sink_parts", (plan.chunks, nd, H, dv), torch.float32)
             ml = ctx.workspace.get("sink_part_sums", (plan.chunks, nd, H, 2), torch.float32)
             if launch_log is not None:
@@ -1262,12 +1261,12 @@ def attention_sink(q, k_cache, v_cache, out, ctx, block_table, H: int, K: int, d
                    "attention (sink, decode)")
             _cost(_size(acc) + nd * H * dv * size * (2 if gate is not None else 1))
             _check(lib.mb_attn_sink_merge(_ptr(acc), _ptr(ml), _ptr(out), _ptr(ctx.seq_lens), _c_int(nd), _c_int(K), _c_int(window),
-                                          _c_int(chunk), _c_int(int(sink)), _ptr(gate), _c_int(gate_stride), _c_int(plan.split), _stream()),
-                   "attention (sink, parts merged)")
+                                          _c_int(chunk), _c_int(int(sink)), _ptr(gate), _c_int(gate_stride), _c_int(plan.split), _ptr(sink_logits),
+                                          _stream()), "attention (sink, parts merged)")
         if ctx.num_requests > nd and launch_log is not None:
             _cost((T - nd) * per_row, 0.0, K * (d + dv) * size, 2.0 * H * (d + dv))
             _pending_cost["rows"] = "prefill"
-        if (ctx.num_requests > nd and use_tc_attention and d == dv and d in (64, 128) and page_size >= 16
+        if (ctx.num_requests > nd and use_tc_attention and d == dv and d in (64, 128) and page_size >= 16 and not values_in_keys
                 and (gate is None or (gate.data_ptr() % 16 == 0 and gate_stride % 8 == 0))):
             # heads of 64 or 128 with values as wide: the tcgen05 kernel that plain causal attention uses takes the chunked
             # mask, the sink and the gate as parameters
@@ -1277,12 +1276,12 @@ def attention_sink(q, k_cache, v_cache, out, ctx, block_table, H: int, K: int, d
                                          _c_int(ctx.max_query_len), _c_int(T), _c_int(K), _c_int(page_size),
                                          ctypes.c_longlong(k_cache.shape[0]), _c_float(scale), _c_int(window),
                                          _ptr(_scratch_for(q.device).error), _c_int(chunk), _c_int(int(sink)), _ptr(gate),
-                                         _c_int(gate_stride), _stream()), "attention (sink, prefill, tensor cores)")
+                                         _c_int(gate_stride), _ptr(sink_logits), _stream()), "attention (sink, prefill, tensor cores)")
         elif ctx.num_requests > nd:
             _check(lib.mb_attn_sink_prefill(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _c_int(max_pages),
                                             _ptr(ctx.cu_tokens), _ptr(ctx.seq_lens), _c_int(nd), _c_int(ctx.num_requests - nd),
                                             _c_int(ctx.max_query_len), _c_int(K), _c_int(page_size), _c_float(scale), _c_int(window),
-                                            _c_int(chunk), _c_int(int(sink)), _ptr(gate), _c_int(gate_stride), _stream()),
+                                            _c_int(chunk), _c_int(int(sink)), _ptr(gate), _c_int(gate_stride), _ptr(sink_logits), _stream()),
                    "attention (sink, prefill)")
         return
     if launch_log is not None:
@@ -1298,28 +1297,32 @@ def attention_sink(q, k_cache, v_cache, out, ctx, block_table, H: int, K: int, d
 use_fast_sink_attention = True
 
 
-def fast_sink_attention_supported(dtype, H: int, K: int, d: int, dv: int) -> bool:
-    return (dtype == torch.bfloat16 and d % 16 == 0 and dv % 16 == 0 and 16 <= d <= 128 and 16 <= dv <= 128
-            and H % K == 0 and 1 <= H // K <= 8)
+def fast_sink_attention_supported(dtype, H: int, K: int, d: int, dv: int, values_in_keys: bool = False) -> bool:
+    """Head sizes in multiples of 16, values up to 128 wide, keys up to 128 (up to 256 where the values are the start of
+    the key rows), at most 8 query heads per kv head."""
+    return (dtype == torch.bfloat16 and d % 16 == 0 and dv % 16 == 0 and 16 <= d <= (256 if values_in_keys else 128) and 16 <= dv <= 128
+            and H % K == 0 and 1 <= H // K <= 8 and (not values_in_keys or dv <= d))
 
 
-def _sink_job(d: int, dv: int, group: int) -> tuple:
-    return (["attention_sink_fast.cu"], [f"HEAD_DIM={d}", f"V_DIM={dv}", f"GROUP={group}"])
+def _sink_job(d: int, dv: int, group: int, values_in_keys: bool = False) -> tuple:
+    return (["attention_sink_fast.cu"], [f"HEAD_DIM={d}", f"V_DIM={dv}", f"GROUP={group}"] + (["V_IN_K"] if values_in_keys else []))
 
 
-def _sink_lib(d: int, dv: int, group: int):
-    return build.load(f"mb_attention_sink_fast_d{d}_v{dv}_g{group}", *_sink_job(d, dv, group))
+def _sink_name(d: int, dv: int, group: int, values_in_keys: bool = False) -> str:
+    return f"mb_attention_sink_fast_d{d}_v{dv}_g{group}" + ("_vk" if values_in_keys else "")
+
+
+def _sink_lib(d: int, dv: int, group: int, values_in_keys: bool = False):
+    return build.load(_sink_name(d, dv, group, values_in_keys), *_sink_job(d, dv, group, values_in_keys))
 
 
 def sink_attention_jobs(dtype, H: int, K: int, d: int, dv: int, values_in_keys: bool = False) -> dict:
     """The kernels a sink-attention mixer of this head layout runs: the head preparation and the plain kernel, and the
     tensor-core kernels compiled for the layout where it allows."""
     jobs = library_jobs("mb_attention_sink")
-    if values_in_keys:
-        return jobs
-    if use_fast_sink_attention and fast_sink_attention_supported(dtype, H, K, d, dv):
-        jobs[f"mb_attention_sink_fast_d{d}_v{dv}_g{H // K}"] = _sink_job(d, dv, H // K)
-        if d == dv and d in (64, 128):
+    if use_fast_sink_attention and fast_sink_attention_supported(dtype, H, K, d, dv, values_in_keys):
+        jobs[_sink_name(d, dv, H // K, values_in_keys)] = _sink_job(d, dv, H // K, values_in_keys)
+        if d == dv and d in (64, 128) and not values_in_keys:
             jobs[f"mb_attention_tc_d{d}_g{H // K}"] = build.attention_tc_job(d, H // K)
     return jobs
 
@@ -1345,7 +1348,7 @@ def sink_decode_plan(dtype, requests: int, H: int, K: int, d: int, dv: int, span
     """Enough chunks for about four CTAs per SM over all requests and kv heads, none shorter than 64 keys.  A token sees at
     most its window or its chunk of keys, whatever the sequence's length: the split follows that, not the context.  None
     where the plain kernel runs (it needs no plan)."""
-    if values_in_keys or not (use_fast_sink_attention and fast_sink_attention_supported(dtype, H, K, d, dv)):
+    if not (use_fast_sink_attention and fast_sink_attention_supported(dtype, H, K, d, dv, values_in_keys)):
         return None
     seen = max(int(span), 1)
     if window > 0:
