@@ -11,7 +11,9 @@
 // in chunk order, which also adds the sink and applies the gate.
 // K pages [page][kv_head][offset][HEAD_DIM], V pages [page][kv_head][offset][V_DIM].
 // -DV_IN_K: there are no value pages; a position's values are the first V_DIM elements of its key row (a latent that keys and
-// values share), so a key block in shared memory serves both products and nothing is fetched twice.
+// values share), so a key block in shared memory serves both products and nothing is fetched twice.  The pages then hold one
+// kv head that every query head reads: the launchers' `K` only counts groups of GROUP query heads (a CTA's rows), so any
+// number of query heads that is a multiple of GROUP can share the rows.
 #define MB_LIB "attention_sink_fast"
 #define MB_LIB_ID 15
 #include "common.cuh"
@@ -74,7 +76,11 @@ __device__ __forceinline__ void load_kv_block(bf16* dst_k, bf16* dst_v, const bf
         const bool is_k = c < CK;
         bf16* dst = is_k ? dst_k + row * LDK + c * 8 : dst_v + row * LDV + (c - CK) * 8;
         if (key <= k_last && key >= k_first) {
+#ifdef V_IN_K
+            const size_t slot = ((size_t)table[key >> page_shift] << page_shift) + (size_t)(key & page_mask);       // one kv head
+#else
             const size_t slot = (((size_t)table[key >> page_shift] * K + kh) << page_shift) + (size_t)(key & page_mask);
+#endif
             cp_async16(dst, is_k ? k_cache + slot * D + c * 8 : v_cache + slot * DV + (c - CK) * 8);
         } else {
             *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);

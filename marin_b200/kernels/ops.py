@@ -1243,7 +1243,12 @@ def attention_sink(q, k_cache, v_cache, out, ctx, block_table, H: int, K: int, d
         return
     size = q.element_size()
     per_row = H * (d + (3 if gate is not None else 2) * dv) * size
+    key_bytes = (d if values_in_keys else K * (d + dv)) * size      # what one cached position holds for this layer
     if use_fast_sink_attention and fast_sink_attention_supported(q.dtype, H, K, d, dv, values_in_keys) and page_size & (page_size - 1) == 0:
+        if values_in_keys:
+            # one kv head that every query head reads: a CTA takes as many query heads as the kernels group, and `K` counts
+            # those groups from here on
+            K = H // sink_group(H, K, True)
         lib = _sink_lib(d, dv, H // K, values_in_keys)
         max_pages = block_table.shape[1]
         nd = ctx.num_decode
@@ -1253,7 +1258,7 @@ def attention_sink(q, k_cache, v_cache, out, ctx, block_table, H: int, K: int, d
             acc = ctx.workspace.get("sink_parts", (plan.chunks, nd, H, dv), torch.float32)
             ml = ctx.workspace.get("sink_part_sums", (plan.chunks, nd, H, 2), torch.float32)
             if launch_log is not None:
-                _cost(nd * per_row + 2 * _size(acc), 0.0, K * (d + dv) * size, 2.0 * H * (d + dv))
+                _cost(nd * per_row + 2 * _size(acc), 0.0, key_bytes, 2.0 * H * (d + dv))
                 _pending_cost["rows"] = "decode"
             _check(lib.mb_attn_sink_decode(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(acc), _ptr(ml), _ptr(block_table),
                                            _c_int(max_pages), _ptr(ctx.seq_lens), _c_int(nd), _c_int(K), _c_int(page_size), _c_float(scale),
@@ -1264,7 +1269,7 @@ def attention_sink(q, k_cache, v_cache, out, ctx, block_table, H: int, K: int, d
                                           _c_int(chunk), _c_int(int(sink)), _ptr(gate), _c_int(gate_stride), _c_int(plan.split), _ptr(sink_logits),
                                           _stream()), "attention (sink, parts merged)")
         if ctx.num_requests > nd and launch_log is not None:
-            _cost((T - nd) * per_row, 0.0, K * (d + dv) * size, 2.0 * H * (d + dv))
+            _cost((T - nd) * per_row, 0.0, key_bytes, 2.0 * H * (d + dv))
             _pending_cost["rows"] = "prefill"
         if (ctx.num_requests > nd and use_tc_attention and d == dv and d in (64, 128) and page_size >= 16 and not values_in_keys
                 and (gate is None or (gate.data_ptr() % 16 == 0 and gate_stride % 8 == 0))):
@@ -1285,7 +1290,7 @@ def attention_sink(q, k_cache, v_cache, out, ctx, block_table, H: int, K: int, d
                    "attention (sink, prefill)")
         return
     if launch_log is not None:
-        _cost(T * per_row, 0.0, K * (d + dv) * size, 2.0 * H * (d + dv))
+        _cost(T * per_row, 0.0, key_bytes, 2.0 * H * (d + dv))
         _pending_cost["rows"] = "all"
     _check(_lib("mb_attention_sink").mb_attention_sink(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _code(q), _ptr(block_table), _c_int(block_table.shape[1]), _ptr(ctx.req_index),
@@ -1297,11 +1302,21 @@ def attention_sink(q, k_cache, v_cache, out, ctx, block_table, H: int, K: int, d
 use_fast_sink_attention = True
 
 
+def sink_group(H: int, K: int, values_in_keys: bool = False) -> int:
+    """Query heads a CTA of the tensor-core kernels takes together: those of one kv head; where every query head reads the
+    same page rows (a shared latent: one kv head), the largest divisor of the head count up to 8."""
+    if not values_in_keys:
+        return H // K
+    return max(g for g in range(1, 9) if H % g == 0)
+
+
 def fast_sink_attention_supported(dtype, H: int, K: int, d: int, dv: int, values_in_keys: bool = False) -> bool:
     """Head sizes in multiples of 16, values up to 128 wide, keys up to 128 (up to 256 where the values are the start of
-    the key rows), at most 8 query heads per kv head."""
+    the key rows), at most 8 query heads per kv head (any number of heads over a shared latent)."""
+    if values_in_keys and K != 1:
+        return False
     return (dtype == torch.bfloat16 and d % 16 == 0 and dv % 16 == 0 and 16 <= d <= (256 if values_in_keys else 128) and 16 <= dv <= 128
-            and H % K == 0 and 1 <= H // K <= 8 and (not values_in_keys or dv <= d))
+            and H % K == 0 and 1 <= sink_group(H, K, values_in_keys) <= 8 and (not values_in_keys or dv <= d))
 
 
 def _sink_job(d: int, dv: int, group: int, values_in_keys: bool = False) -> tuple:
@@ -1321,7 +1336,8 @@ def sink_attention_jobs(dtype, H: int, K: int, d: int, dv: int, values_in_keys: 
     tensor-core kernels compiled for the layout where it allows."""
     jobs = library_jobs("mb_attention_sink")
     if use_fast_sink_attention and fast_sink_attention_supported(dtype, H, K, d, dv, values_in_keys):
-        jobs[_sink_name(d, dv, H // K, values_in_keys)] = _sink_job(d, dv, H // K, values_in_keys)
+        g = sink_group(H, K, values_in_keys)
+        jobs[_sink_name(d, dv, g, values_in_keys)] = _sink_job(d, dv, g, values_in_keys)
         if d == dv and d in (64, 128) and not values_in_keys:
             jobs[f"mb_attention_tc_d{d}_g{H // K}"] = build.attention_tc_job(d, H // K)
     return jobs
@@ -1350,6 +1366,7 @@ def sink_decode_plan(dtype, requests: int, H: int, K: int, d: int, dv: int, span
     where the plain kernel runs (it needs no plan)."""
     if not (use_fast_sink_attention and fast_sink_attention_supported(dtype, H, K, d, dv, values_in_keys)):
         return None
+    K = H // sink_group(H, K, values_in_keys)          # CTAs per request and chunk
     seen = max(int(span), 1)
     if window > 0:
         seen = min(seen, window)

@@ -553,14 +553,14 @@ class LatentAttention(Mixer):
         pos = self.position
         ops.latent_finish(rows, q, self.c_weight, self.norm_eps, ctx.positions, pos.inv_freq, pos.rotary_dim, pos.interleaved,
                           cache.slot_mapping, cache.k, H, dn, dr, r, writes)
-        ops.stage_name = "queries into the latent"
+        ops.stage_name = "q into the latent"
         ops.heads_product(rows, self.q_head, dn, self.w_uk_t, q, D)
         mixed = ws.get("latent_out", (T, H * r), x.dtype)
         ops.stage_name = "attention"
         plans = ctx.decode_plans
         ops.attention_sink(q, cache.k, cache.k, mixed, ctx, cache.block_table, H, 1, D, r, self.scale, 0, 0, self.sink, None,
                            plans.get(self.decode_plan_key()) if plans else None, self.sink_logits)
-        ops.stage_name = "values from the latent"
+        ops.stage_name = "v from the latent"
         out = ws.get("attn_out", (T, self.o_dim), x.dtype)
         ops.heads_product(mixed, r, r, self.w_uv, out, self.v_head_dim)
         ops.stage_name = "o"

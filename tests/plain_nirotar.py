@@ -46,9 +46,11 @@ def pair_frequencies(rot: dict) -> torch.Tensor:
     return torch.tensor(out, dtype=F64)
 
 
-def rotate_pairs(x: torch.Tensor, positions: torch.Tensor, rot: dict) -> torch.Tensor:
+def rotate_pairs(x: torch.Tensor, positions: torch.Tensor, rot: Optional[dict]) -> torch.Tensor:
     """``x`` ``[T, heads, dim]``: of every head the first ``dims`` elements turn, element ``2i`` together with ``2i + 1``, by
-    the angle ``p f_i``; the rest pass."""
+    the angle ``p f_i``; the rest pass.  Without ``rot`` nothing turns."""
+    if not rot or not int(rot["dims"]):
+        return x
     dims = int(rot["dims"])
     ang = positions.to(F64)[:, None] * pair_frequencies(rot)[None, :]
     cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
@@ -97,7 +99,7 @@ def latent_of(h: torch.Tensor, positions: torch.Tensor, W: Dict[str, torch.Tenso
     r = int(m["kv_rank"])
     both = h @ f64(W[pre + "dkv"]).T
     c = rms_norm(both[:, :r], W[pre + "dkv.norm"], eps)
-    k_rot = rotate_pairs(both[:, None, r:], positions, m["rot"])[:, 0]
+    k_rot = rotate_pairs(both[:, None, r:], positions, m.get("rot"))[:, 0]
     return c, k_rot
 
 
@@ -107,7 +109,7 @@ def latent_attention(h: torch.Tensor, positions: torch.Tensor, W: Dict[str, torc
     H, d, dr, dv, r = int(m["heads"]), int(m["dim"]), int(m["rot_dim"]), int(m["vdim"]), int(m["kv_rank"])
     T = h.shape[0]
     q = (h @ f64(W[pre + "q"]).T).view(T, H, d + dr)
-    q_rot = rotate_pairs(q[..., d:], positions, m["rot"])
+    q_rot = rotate_pairs(q[..., d:], positions, m.get("rot"))
     k_up = (c @ f64(W[pre + "uk"]).T).view(T, H, d)
     v_up = (c @ f64(W[pre + "uv"]).T).view(T, H, dv)
     sink = f64(W[pre + "sink"])
