@@ -2,7 +2,7 @@
 """Decode and prefill throughput of the engine on one B200, with their fractions of roofline.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers N] [--impl ours|reference]
-    python bench.py --arch lakulix|fegarax [--model 4b|8b|14b] [--layers 12] [--batch 8] [--profile]
+    python bench.py --arch lakulix|fegarax|nirotar [--model 4b|8b|14b] [--layers 12] [--batch 8] [--profile]
 
 The default run has the layer sizes of the Qwen3-4B layout with random bfloat16 weights, a batch of 8
 sequences and a context of 4096 positions (the last timed step reaches it).  A "step" is one decode
@@ -21,7 +21,10 @@ Lakulix layers (linear attention, sigmoid attention, time mixing, in turn; a Pol
 layout's sizes, decode at the given batch and the prompt step, each with its fraction of roofline, as one JSON line of
 its own form (``--profile``: its stage tables).  ``--arch fegarax`` does the same for Fegarax layers (four residual streams,
 attention with the layout's heads, a gate and a sink, eight experts of half the feed-forward width of which two are chosen).
-The default workload and its line are not touched by either.
+``--arch nirotar`` measures Nirotar layers (windowed attention with a learned sink and attention over a shared latent in turn,
+experts without a gate chosen by a table over the token ids, a shared expert) beside the Fegarax layout of the same width,
+depth, vocabulary and heads, the closest of the engine's models (attention with a sink, routed experts).
+The default workload and its line are not touched by any of them.
 
 Peaks come from MEASURED_PEAKS.json beside this file if present, else 6.65 TB/s and 1.59 PFLOP/s.
 Between timed iterations nothing is flushed: a decode step reads gigabytes of weights, far more than the
@@ -275,7 +278,8 @@ def profile_mode(engine, args, pk, label=None, batches=None):
             runner.begin(rid)
             engine.cache.reserve(rid, CONTEXT - steps - warmup)
             engine.cache.commit(rid, CONTEXT - steps - warmup)
-        rows = profile_steps(runner, lambda i: [StepEntry(rid, [5 + i], [0]) for rid in ids], steps, warmup)
+        # (token ids that differ between the requests: a model that chooses experts by the token id should not send them all to the same ones)
+        rows = profile_steps(runner, lambda i: [StepEntry(rid, [(5 + i + 7919 * k) % vocab], [0]) for k, rid in enumerate(ids)], steps, warmup)
         print(format_table(rows, pk["hbm_gbs"], pk["bf16_tflops"], f"decode step, batch {batch}, sequences of about {CONTEXT} positions"))
         print()
         for rid in ids:
@@ -334,6 +338,36 @@ def fegarax_layout(raw: dict, layers: int) -> dict:
             "norm": {"eps": 1e-6}, "max_positions": 2 * CONTEXT, "layers": [{"type": "attention", "mixer": mixer, "mlp": mlp} for _ in range(layers)]}
 
 
+NIROTAR_LAYERS = ("in turn: attention with the layout's heads (a window of 1,024 positions, neighbouring pairs rotated over half of every "
+                  "head with band-scaled frequencies, a learned sink); attention over a shared latent (as many heads, 64 unrotated + 32 "
+                  "rotated query numbers, values of 64, page rows of 128 + 32 numbers, a learned sink); attention again; latent attention "
+                  "that reads the rows of the latent layer two before it.  8 experts without a gate (squared relu) of 5/8 of the layout's "
+                  "feed-forward width, 2 chosen by a table over the token ids, and a shared expert: as many active feed-forward weights "
+                  "per token as the Fegarax and the dense layouts")
+
+
+def nirotar_layout(raw: dict, layers: int) -> dict:
+    """A Nirotar configuration at a Qwen3 layout's sizes: the same width, vocabulary and attention heads; experts and a
+    shared expert that together activate as many feed-forward weights per token as the layout's dense feed-forward."""
+    head, heads = raw["head_dim"], raw["num_attention_heads"]
+    attention = {"heads": heads, "kv_heads": raw["num_key_value_heads"], "dim": head, "vdim": head, "scale": head ** -0.5,
+                 "mask": {"size": 1024},
+                 "rot": {"base": 500000.0, "dims": head // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 2048}}}
+    latent = {"heads": heads, "dim": 64, "rot_dim": 32, "vdim": 64, "kv_rank": 128, "scale": 96 ** -0.5, "rot": {"base": 500000.0, "dims": 32}}
+    half = raw["intermediate_size"] // 2
+    expert = half * 5 // 4 // 64 * 64
+    shared = (6 * half - 4 * expert) // 2 // 64 * 64
+    mlp = {"kind": "moe", "expert": {"ff": expert}, "router": {"experts": 8, "top": 2}, "shared": {"ff": shared}}
+    out = []
+    for i in range(layers):
+        if i % 2 == 0:
+            out.append({"type": "attention", "mixer": attention, "mlp": mlp})
+        else:
+            out.append({"type": "latent_attention", "mixer": dict(latent, **({"kv_from": i - 2} if i % 4 == 3 else {})), "mlp": mlp})
+    return {"architecture": "Nirotar", "vocab": raw["vocab_size"], "width": raw["hidden_size"], "norm": {"eps": 1e-6},
+            "max_positions": 2 * CONTEXT, "layers": out}
+
+
 def arch_mode(args, pk, arch: str) -> int:
     """Decode and prompt throughput of another architecture at a Qwen3 layout's sizes, and of that Qwen3 layout at the same
     depth, with their fractions of roofline: one JSON line.  With --profile: the architecture's stage tables."""
@@ -342,14 +376,21 @@ def arch_mode(args, pk, arch: str) -> int:
     import torch
 
     from marin_b200 import Engine
-    from marin_b200.config import FegaraxConfig, LakulixConfig, Qwen3Config
+    from marin_b200.config import FegaraxConfig, LakulixConfig, NirotarConfig, Qwen3Config
 
     layers = args.layers or 12
     raw = dict(LAYOUTS[args.model], num_hidden_layers=layers)
     warmup = max(3, args.warmup)
     title = arch.capitalize()
-    other = LakulixConfig.from_dict(lakulix_layout(raw, layers)) if arch == "lakulix" else FegaraxConfig.from_dict(fegarax_layout(raw, layers))
-    arms = {arch: other, "qwen3": Qwen3Config.from_dict(raw)}
+    # the model it is measured beside: the Qwen3 layout, or for Nirotar the engine's closest model, Fegarax at that layout's sizes
+    beside = "fegarax" if arch == "nirotar" else "qwen3"
+    if arch == "lakulix":
+        other = LakulixConfig.from_dict(lakulix_layout(raw, layers))
+    elif arch == "fegarax":
+        other = FegaraxConfig.from_dict(fegarax_layout(raw, layers))
+    else:
+        other = NirotarConfig.from_dict(nirotar_layout(raw, layers))
+    arms = {arch: other, beside: FegaraxConfig.from_dict(fegarax_layout(raw, layers)) if beside == "fegarax" else Qwen3Config.from_dict(raw)}
     out = {}
     for name, cfg in arms.items():
         if args.profile and name != arch:
@@ -382,16 +423,16 @@ def arch_mode(args, pk, arch: str) -> int:
         gc.collect()
         torch.cuda.empty_cache()
     print(json.dumps({
-        "metric": f"{title} beside the Qwen3-{args.model.upper()} layout at equal width, depth and vocabulary: decode tok/s at batch {args.batch} "
+        "metric": f"{title} beside the {'Fegarax layers at the ' if beside == 'fegarax' else ''}Qwen3-{args.model.upper()} layout at equal width, depth and vocabulary: decode tok/s at batch {args.batch} "
                   f"(context {CONTEXT}), prefill tok/s at {PREFILL_TOKENS} tokens, fractions of roofline",
         "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup, "dtype": "bf16", "higher_is_better": True,
         "data": "synthetic (uniform random token ids, seeded random weights)", "peaks": pk,
         "config": {"layers": layers, "width": raw["hidden_size"], "ff": raw["intermediate_size"], "vocab": raw["vocab_size"],
                    "global_batch": args.batch, "seq_len": CONTEXT, "prefill_tokens": PREFILL_TOKENS, "kv_block": PAGE,
-                   f"{arch}_layers": FEGARAX_LAYERS if arch == "fegarax" else
+                   f"{arch}_layers": FEGARAX_LAYERS if arch == "fegarax" else NIROTAR_LAYERS if arch == "nirotar" else
                    "lightning (heads of 128 x 128), attention (the layout's heads), wkv (heads of 64) in turn, a dense feed-forward in each",
                    "l2": "inputs larger than L2 (weights read per step exceed 126 MB)"},
-        arch: out[arch], "qwen3": out["qwen3"], "impl": "ours"}))
+        arch: out[arch], beside: out[beside], "impl": "ours"}))
     return 0
 
 
@@ -416,8 +457,9 @@ def main() -> int:
     ap.add_argument("--model", default="4b", choices=sorted(LAYOUTS), help="layer sizes: Qwen3-4B (the default), 8B or 14B layout")
     ap.add_argument("--context", type=int, default=CONTEXT, help="context length the last timed decode step reaches (default 4096)")
     ap.add_argument("--profile", action="store_true", help="print where a step's time goes, stage by stage, instead of the JSON line")
-    ap.add_argument("--arch", default="qwen3", choices=["qwen3", "lakulix", "fegarax"],
-                    help="qwen3: the default workload; lakulix, fegarax: that architecture at the layout's sizes beside the Qwen3 layout of equal size")
+    ap.add_argument("--arch", default="qwen3", choices=["qwen3", "lakulix", "fegarax", "nirotar"],
+                    help="qwen3: the default workload; lakulix, fegarax: that architecture at the layout's sizes beside the Qwen3 layout of "
+                         "equal size; nirotar: beside the Fegarax layers at that layout's sizes")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()

@@ -110,9 +110,11 @@ MB_API int mb_latent_finish(const void* row, int row_stride, int dtype, void* q_
 
 // ---- a product per head: out[t][a][n] = sum_k w[a][n][k] x[t][a][k] -------------------------------------------------------
 // x: element (t, a, k) at x + t x_ld + a x_head + k;  w: [H][N][K];  out: element (t, a, n) at out + t o_ld + a o_head + n.
-// Plain kernel: a block per (token, head); a warp per output column, lanes along k in a fixed order, so a token's result
-// does not depend on the batch.
+// Plain kernel: a block per (token, head, run of HP_COLS output columns); a warp per column, lanes along k in a fixed order,
+// so a token's result does not depend on the batch.  (Few tokens bring few blocks otherwise: a single-token step of eight
+// requests took 28 us for a product of half a megabyte of weights with one block per token and head.)
 #define HP_THREADS 128
+#define HP_COLS 16
 template <typename T>
 __global__ void __launch_bounds__(HP_THREADS) heads_product_kernel(const T* __restrict__ x, int x_ld, int x_head, const T* __restrict__ w,
                                                                    T* __restrict__ out, int o_ld, int o_head, int N, int K) {
@@ -126,7 +128,8 @@ __global__ void __launch_bounds__(HP_THREADS) heads_product_kernel(const T* __re
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const T* wa = w + (size_t)a * N * K;
     T* dst = out + (size_t)t * o_ld + (size_t)a * o_head;
-    for (int n = warp; n < N; n += HP_THREADS / 32) {
+    const int n_end = min(N, (int)(blockIdx.z + 1) * HP_COLS);
+    for (int n = blockIdx.z * HP_COLS + warp; n < n_end; n += HP_THREADS / 32) {
         const T* wr = wa + (size_t)n * K;
         float dot = 0.0f;
         for (int k = lane; k < K; k += 32) dot = fmaf(xs[k], to_f32(wr[k]), dot);
@@ -222,7 +225,7 @@ MB_API int mb_heads_product(const void* x, int x_ld, int x_head, const void* w, 
         aligned16(w) && (((uintptr_t)out) & 3) == 0 && tokens >= 16)
         return launch_kernel(heads_product_tc_kernel, dim3((tokens + HT_M - 1) / HT_M, (N + HT_N - 1) / HT_N, H), 128, 0, s, 0, (const bf16*)x,
                              x_ld, x_head, (const bf16*)w, (bf16*)out, o_ld, o_head, tokens, N, K);
-    dim3 grid(tokens, H);
+    dim3 grid(tokens, H, (N + HP_COLS - 1) / HP_COLS);
     if (dtype == MB_F32)
         return launch_kernel(heads_product_kernel<float>, grid, HP_THREADS, (size_t)K * 4, s, 0, (const float*)x, x_ld, x_head, (const float*)w,
                              (float*)out, o_ld, o_head, N, K);

@@ -91,7 +91,11 @@ __device__ __forceinline__ void cluster_reduce_rows4(uint32_t red_addr, void* ou
                         *reinterpret_cast<__nv_bfloat162*>(&packed.y) = __floats2bfloat162_rn(nv[2] * (gain[u].z + o1), nv[3] * (gain[u].w + o1));
                         *reinterpret_cast<uint2*>(norm.scaled + at) = packed;
                     }
-                } else if (mode == TC_OUT_BF16) {
+                } else if (mode == TC_OUT_BF16 || mode == TC_OUT_RELU2) {
+                    if (mode == TC_OUT_RELU2) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) sum[e] = relu2_of(sum[e]);
+                    }
                     uint2 packed;
                     *reinterpret_cast<__nv_bfloat162*>(&packed.x) = __floats2bfloat162_rn(sum[0], sum[1]);
                     *reinterpret_cast<__nv_bfloat162*>(&packed.y) = __floats2bfloat162_rn(sum[2], sum[3]);
@@ -1122,7 +1126,7 @@ static int persistent_dispatch(const void* x, const void* w, void* out, int mode
                                const TcHeadsOut& heads = TcHeadsOut{}, const float* rope = nullptr) {
     if (T <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ctas <= 0) return MB_ERR_BAD_SIZE;
-    if (mode < 0 || mode > 3 || (mode == 3 && N % 32 != 0)) return MB_ERR_BAD_DTYPE;
+    if (mode < 0 || mode > 4 || (mode == 3 && N % 32 != 0)) return MB_ERR_BAD_DTYPE;
     if (norm.weight != nullptr && (mode != TC_OUT_F32_ACC || norm.scaled == nullptr || norm.sumsq == nullptr)) return MB_ERR_BAD_DTYPE;
     if (scale.sumsq != nullptr && (scale.slots <= 0 || scale.dim <= 0)) return MB_ERR_BAD_SIZE;
     CUtensorMap mw, mx;
@@ -1223,7 +1227,7 @@ static int gemm_tc_dispatch(const void* x, const void* w, void* out, int mode, i
     if (norm.weight != nullptr && !cluster_reduce && splits > 1) return MB_ERR_BAD_SIZE;
     if (scale.sumsq != nullptr && (scale.slots <= 0 || scale.dim <= 0 || (!cluster_reduce && splits > 1))) return MB_ERR_BAD_SIZE;
     if (K <= 0 || K % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return MB_ERR_BAD_SIZE;
-    if (mode < 0 || mode > 3 || (mode == 3 && (splits > 1 || N % 32 != 0))) return MB_ERR_BAD_DTYPE;
+    if (mode < 0 || mode > 4 || (mode == 3 && (splits > 1 || N % 32 != 0))) return MB_ERR_BAD_DTYPE;
     const int total_kb = (K + TC_BK - 1) / TC_BK;
     if (splits < 1) splits = 1;
     if (splits > total_kb) splits = total_kb;

@@ -10,6 +10,9 @@
 #define TC_OUT_F32 1
 #define TC_OUT_F32_ACC 2
 #define TC_OUT_SWIGLU 3       // w holds gate and up rows interleaved in blocks of 16; out [T, N/2] bf16 = silu(gate) * up
+#define TC_OUT_RELU2 4        // out bf16 = max(x w^T, 0)^2: the activation of a feed-forward without a gate
+
+__device__ __forceinline__ float relu2_of(float v) { v = fmaxf(v, 0.0f); return v * v; }
 
 template <int BN>
 struct TcSmem {
@@ -20,6 +23,7 @@ struct TcSmem {
 
 __device__ __forceinline__ void store_out(void* out, int mode, size_t at, float v) {
     if (mode == TC_OUT_BF16) ((bf16*)out)[at] = __float2bfloat16_rn(v);
+    else if (mode == TC_OUT_RELU2) ((bf16*)out)[at] = __float2bfloat16_rn(relu2_of(v));
     else if (mode == TC_OUT_F32) ((float*)out)[at] = v;
     else ((float*)out)[at] += v;
 }
@@ -40,6 +44,11 @@ __device__ __forceinline__ void store_chunk(void* out, int mode, int t_first, in
 #pragma unroll
         for (int j = 0; j < 16; ++j)
             if (t_first + j < T) o[(size_t)(t_first + j) * N + n] = __float2bfloat16_rn(v[j]);
+    } else if (mode == TC_OUT_RELU2) {
+        bf16* o = (bf16*)out;
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+            if (t_first + j < T) o[(size_t)(t_first + j) * N + n] = __float2bfloat16_rn(relu2_of(v[j]));
     } else {
         float* o = (float*)out;
 #pragma unroll

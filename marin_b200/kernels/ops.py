@@ -396,9 +396,12 @@ class NormedRows:
 COUPLED_NORM_MAX_TOKENS = 16
 
 
-def gemm(x, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False, then_norm: Optional[NormOut] = None):
+def gemm(x, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False, then_norm: Optional[NormOut] = None,
+         activation: Optional[str] = None):
     """``out[t, n] (+)= sum_k x[t, k] * w[n, k]``.  bfloat16 inputs run on the tensor cores (tcgen05, float32
-    accumulate); float32 inputs run on the CUDA cores in true float32.
+    accumulate); float32 inputs run on the CUDA cores in true float32.  ``activation`` "relu2": ``out = max(x w^T, 0)^2`` in
+    the activation dtype, applied to the float32 sums in the tensor-core product's epilogue (as a kernel of its own behind
+    the plain product).
 
     ``then_norm`` (with ``accumulate``) asks for the RMS norm of the updated ``out``: if this product can carry it,
     a ``NormedRows`` is returned for the next product to finish; otherwise None, and the caller runs the norm."""
@@ -415,6 +418,10 @@ def gemm(x, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False, then_n
     if (use_tensor_cores and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and K % 8 == 0
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and T > 0):
         mode = 2 if accumulate else (0 if out.dtype == torch.bfloat16 else 1)
+        if activation is not None:
+            if activation != "relu2" or accumulate or out.dtype != torch.bfloat16 or then_norm is not None:
+                raise KernelError(f"gemm: activation {activation!r} goes with a plain bfloat16 output")
+            mode = 4
         if many_tokens(T, N):
             s = _scratch_for(x.device)
             lib = _lib("mb_gemm_tc")
@@ -459,6 +466,10 @@ def gemm(x, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False, then_n
     assert scaled is None, "rows with a pending norm reach only the tensor-core product"
     _check(_lib("mb_gemm_simple").mb_gemm_simple(_ptr(x), _code(x), _ptr(w), _code(w), _ptr(out), _code(out), _c_int(T),
                                                 _c_int(N), _c_int(K), _c_int(int(accumulate)), _stream()), "gemm")
+    if activation is not None:
+        if activation != "relu2" or accumulate:
+            raise KernelError(f"gemm: activation {activation!r} goes with a plain output")
+        relu2(out)
     return None
 
 
@@ -770,11 +781,10 @@ def gemm_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor, out: torch.Tensor,
 
 def gemm_act(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, activation: str = "relu2") -> None:
     """``out = act(x w^T)`` in the activation dtype, for a feed-forward without a gate (``activation`` "relu2": the square of
-    relu).  The product, then the activation in place over its result."""
+    relu).  The tensor-core product applies it in its epilogue; behind the plain product it runs in place over the result."""
     if activation != "relu2":
         raise KernelError(f"gemm_act: unknown activation {activation!r}")
-    gemm(x, w, out)
-    relu2(out)
+    gemm(x, w, out, activation=activation)
 
 
 def gather_rows(src: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
@@ -1248,13 +1258,13 @@ def attention_sink(q, k_cache, v_cache, out, ctx, block_table, H: int, K: int, d
         if values_in_keys:
             # one kv head that every query head reads: a CTA takes as many query heads as the kernels group, and `K` counts
             # those groups from here on
-            K = H // sink_group(H, K, True)
+            K = H // sink_group(H, 1, True)
         lib = _sink_lib(d, dv, H // K, values_in_keys)
         max_pages = block_table.shape[1]
         nd = ctx.num_decode
         if nd > 0:
             if plan is None:
-                plan = sink_decode_plan(q.dtype, nd, H, K, d, dv, ctx.max_seq_len, window, chunk, values_in_keys)
+                plan = sink_decode_plan(q.dtype, nd, H, 1 if values_in_keys else K, d, dv, ctx.max_seq_len, window, chunk, values_in_keys)
             acc = ctx.workspace.get("sink_parts", (plan.chunks, nd, H, dv), torch.float32)
             ml = ctx.workspace.get("sink_part_sums", (plan.chunks, nd, H, 2), torch.float32)
             if launch_log is not None:

@@ -407,6 +407,23 @@ def test_products_per_head_over_strided_rows(dtype, T, H, N, K):
     torch.testing.assert_close(got[:, :, :N].double(), want, **(dict(rtol=1e-5, atol=1e-5) if dtype == "float32" else dict(rtol=2e-2, atol=2e-2)))
 
 
+@pytest.mark.parametrize("T", [1, 8, 40, 200, 2100])
+def test_the_product_applies_the_squared_relu(T):
+    """bfloat16: the tensor-core product squares the positive part of its float32 sums before it rounds them; float32: the
+    same through the plain product and the activation's own kernel."""
+    from marin_b200.kernels import ops
+
+    g = torch.Generator().manual_seed(T)
+    x, w = torch.randn(T, 192, generator=g), torch.randn(320, 192, generator=g) / math.sqrt(192)
+    for td, tol in ((torch.bfloat16, dict(rtol=2e-2, atol=2e-2)), (torch.float32, dict(rtol=1e-5, atol=1e-5))):
+        xd, wd = x.to(td), w.to(td)
+        want = torch.relu(xd.double() @ wd.double().T) ** 2
+        out = torch.empty(T, 320, dtype=td, device=DEV)
+        ops.gemm_act(xd.to(DEV), wd.to(DEV), out, "relu2")
+        torch.testing.assert_close(out.double().cpu(), want, **tol)
+        assert float(out.min()) >= 0.0 and bool((out == 0).any())
+
+
 # ---- whole models -----------------------------------------------------------------------------------------------------
 
 class Case:
