@@ -1,5 +1,7 @@
 // Prefill attention on the 5th-generation tensor cores (tcgen05 / TMEM), compiled per head size (-DHEAD_DIM=64|128)
-// and group size (-DGROUP).  A CTA takes 128 consecutive query tokens of one request and one query head and
+// and group size (-DGROUP).  With -DV_IN_K the values are the first V_DIM (64 or 128) elements of the key rows (a latent
+// that keys and values share: one kv head, HEAD_DIM any multiple of 16 from 64 to 192): nothing is loaded for V, the
+// P V product reads the key tile again, and the tile is free once that product is done.  A CTA takes 128 consecutive query tokens of one request and one query head and
 // walks the keys in blocks of 64:
 //   S = Q K^T      tcgen05.mma, M = 128 queries, N = 64 keys, K = HEAD_DIM; Q and K tiles in shared memory (TMA,
 //                  128-byte swizzle, K-major); the accumulator S is 64 columns of tensor memory;
@@ -38,17 +40,34 @@
 #ifndef GROUP
 #error "compile with -DGROUP=<query heads per kv head>"
 #endif
+#ifndef V_DIM
+#define V_DIM HEAD_DIM
+#endif
+#ifdef V_IN_K
+static_assert(HEAD_DIM % 16 == 0 && HEAD_DIM >= 64 && HEAD_DIM <= 192, "key rows of 64 to 192 elements, a multiple of 16");
+static_assert((V_DIM == 64 || V_DIM == 128) && V_DIM <= HEAD_DIM, "values are the first 64 or 128 elements of the key rows");
+#define TA_V_IN_K 1
+#else
 static_assert(HEAD_DIM == 64 || HEAD_DIM == 128, "the tcgen05 attention kernel takes heads of 64 or 128");
+static_assert(V_DIM == HEAD_DIM, "values as wide as the keys");
+#define TA_V_IN_K 0
+#endif
 
 #define D HEAD_DIM
-#define NH (D / 64)                    // 64-column halves of a head: one 128-byte swizzle row each
+#define DV V_DIM
+#define NH ((D + 63) / 64)             // 64-column panels of a query or key row: one 128-byte swizzle row each (the last
+                                       // may be partly filled: the copy zero-fills past the row's end, no MMA reads there)
+#define NHV (DV / 64)
 #define TA_BM 128
 #define TA_BN 64
 #define TA_Q_BYTES (NH * TA_BM * 128)
-#define TA_KV_BYTES (NH * TA_BN * 128)  // one of K or V, one buffer
+#define TA_K_BYTES (NH * TA_BN * 128)   // a block of keys
+#define TA_V_BYTES (NHV * TA_BN * 128)  // a block of values
+#define TA_V_OFF (TA_V_IN_K ? 0 : TA_K_BYTES)                   // where a buffer's values start
+#define TA_BUF_BYTES (TA_K_BYTES + (TA_V_IN_K ? 0 : TA_V_BYTES)) // one buffer: K then V, or the rows that are both
 #define TA_PAGE_CACHE 1024            // page ids of a tile's keys kept in shared memory (more are read from global memory)
-#define TA_SMEM (TA_Q_BYTES + 4 * TA_KV_BYTES + 256)
-#define TA_TMEM_COLS 256               // two S buffers of 64 columns, then O: HEAD_DIM columns
+#define TA_SMEM (TA_Q_BYTES + 2 * TA_BUF_BYTES + 256)
+#define TA_TMEM_COLS 256               // two S buffers of 64 columns, then O: V_DIM columns
 #define TA_O_COL (2 * TA_BN)
 
 __device__ __forceinline__ float ta_exp2(float x) {
@@ -202,7 +221,7 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_tc_kernel(
     extern __shared__ __align__(1024) uint8_t smem[];     // the swizzled tiles need 1024-byte alignment (checked below)
     uint8_t* sQ = smem;
     uint8_t* sKV = sQ + TA_Q_BYTES;                       // [buffer][K then V][half][64 rows][128 B]
-    uint64_t* bars = (uint64_t*)(sKV + 4 * TA_KV_BYTES);
+    uint64_t* bars = (uint64_t*)(sKV + 2 * TA_BUF_BYTES);
     uint64_t* q_full = bars;              // Q tile has landed
     uint64_t* k_full = bars + 1;          // [2] a block of K has landed
     uint64_t* v_full = bars + 3;          // [2] a block of V has landed
@@ -259,7 +278,7 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_tc_kernel(
     const int rot = (int)(((unsigned)(h * gridDim.x + qt) * 37u) % (unsigned)nblk);
     auto block_of = [&](int i) { const int j = i + rot; return kb_first + (j >= nblk ? j - nblk : j); };
 
-    if (warp == 5 || warp == 6) {
+    if (warp == 5 || (warp == 6 && !TA_V_IN_K)) {
         // ---- the loader warps: warp 5 asks for Q once and then for every block of K, warp 6 for every block of V, each
         // as soon as the block's buffer is free.  Lanes 0..3 each ask for one box of a block, so that one instruction
         // starts four TMA copies.  (Measured with cycle stamps: asking for a block takes a warp about 900 cycles, issuing
@@ -280,13 +299,18 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_tc_kernel(
             return (int)((((size_t)page_id * K + kh) << page_shift) + (size_t)(key & page_mask));
         };
         auto load_block = [&](int j, int row) {
-            uint8_t* dst = sKV + (size_t)(j & 1) * 2 * TA_KV_BYTES + (keys ? 0 : TA_KV_BYTES);
+            uint8_t* dst = sKV + (size_t)(j & 1) * TA_BUF_BYTES + (keys ? 0 : TA_V_OFF);
             uint64_t* bar = keys ? &k_full[j & 1] : &v_full[j & 1];
-            if (lane == 0) mbar_expect_tx(bar, TA_KV_BYTES);
+            if (lane == 0) mbar_expect_tx(bar, keys ? TA_K_BYTES : TA_V_BYTES);
             __syncwarp();
             if (g < TA_BN) {
+                if (keys) {
 #pragma unroll
-                for (int hf = 0; hf < NH; ++hf) tma_load_2d(dst + hf * (TA_BN * 128) + g * 128, map, hf * 64, row, bar);
+                    for (int hf = 0; hf < NH; ++hf) tma_load_2d(dst + hf * (TA_BN * 128) + g * 128, map, hf * 64, row, bar);
+                } else {
+#pragma unroll
+                    for (int hf = 0; hf < NHV; ++hf) tma_load_2d(dst + hf * (TA_BN * 128) + g * 128, map, hf * 64, row, bar);
+                }
             }
         };
         if (keys && lane == 0) {
@@ -295,8 +319,9 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_tc_kernel(
             for (int hf = 0; hf < NH; ++hf) tma_load_2d(sQ + hf * (TA_BM * 128), &map_q, h * D + hf * 64, tok0 + qt * TA_BM, q_full);
         }
         load_block(0, row_of(0));
-        // the K buffer of block j is free once S of block j - 2 is done, the V buffer once P V of block j - 2 is
-        uint64_t* freed = keys ? s_done : v_free;
+        // the K buffer of block j is free once S of block j - 2 is done, the V buffer once P V of block j - 2 is (rows
+        // that are keys and values both: once P V is)
+        uint64_t* freed = (keys && !TA_V_IN_K) ? s_done : v_free;
         bool ok = true;
         unsigned idle = 0;
         const long long start = clock64();
@@ -326,7 +351,7 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_tc_kernel(
                 qdesc[kk] = umma_desc(sq + (kk / 4) * (TA_BM * 128)) + 2 * (kk % 4);
 #pragma unroll
                 for (int b = 0; b < 2; ++b)
-                    kdesc[b][kk] = umma_desc(smem_u32(sKV + (size_t)b * 2 * TA_KV_BYTES) + (kk / 4) * (TA_BN * 128)) + 2 * (kk % 4);
+                    kdesc[b][kk] = umma_desc(smem_u32(sKV + (size_t)b * TA_BUF_BYTES) + (kk / 4) * (TA_BN * 128)) + 2 * (kk % 4);
             }
             bool ok = wait_or_abort(q_full, 0, abort, error_flag, 21);
             const long long start = TA_T();
@@ -349,17 +374,19 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_tc_kernel(
             }
             TA_OUT(3, m_idle); TA_OUT(4, TA_T() - start); TA_OUT(5, (long long)nblk);
         }
+    } else if (warp == 6) {
+        // (rows that are keys and values both: nothing to ask for)
     } else if (warp == 7) {
         // ---- the issuer of P V: O += P(i) V(i) once the rows have put P(i) into tensor memory and the values have landed
         // (any rescaling of O by the rows happened before they arrived) ----
         if (lane == 0) {
-            constexpr uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(TA_BM >> 4) << 24);
+            constexpr uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(DV >> 3) << 17) | ((uint32_t)(TA_BM >> 4) << 24);
             uint64_t vdesc[2][TA_BN / 16];
 #pragma unroll
             for (int kk = 0; kk < TA_BN / 16; ++kk)
 #pragma unroll
                 for (int b = 0; b < 2; ++b)
-                    vdesc[b][kk] = umma_desc_mn(smem_u32(sKV + (size_t)b * 2 * TA_KV_BYTES) + TA_KV_BYTES + kk * 2048, TA_BN * 128);
+                    vdesc[b][kk] = umma_desc_mn(smem_u32(sKV + (size_t)b * TA_BUF_BYTES) + TA_V_OFF + kk * 2048, TA_BN * 128);
             bool ok = true;
             const long long start = TA_T();
             long long m_idle = 0;
@@ -367,7 +394,8 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_tc_kernel(
                 const int buf = i & 1;
                 const long long m_t0 = TA_T();
                 ok = wait_or_abort(&p_ready[buf], (i >> 1) & 1, abort, error_flag, 29);
-                if (ok) ok = wait_or_abort(&v_full[buf], (i >> 1) & 1, abort, error_flag, 29);
+                // (rows that are keys and values both landed before S was issued: the wait returns at once)
+                if (ok) ok = wait_or_abort(TA_V_IN_K ? &k_full[buf] : &v_full[buf], (i >> 1) & 1, abort, error_flag, 29);
                 m_idle += TA_T() - m_t0;
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -441,7 +469,7 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_tc_kernel(
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-                for (int c = 0; c < D / 32; ++c) {
+                for (int c = 0; c < DV / 32; ++c) {
                     float ov[32];
                     tmem_ld32(lane_base + TA_O_COL + c * 32, ov);
 #pragma unroll
@@ -488,10 +516,10 @@ __global__ void __launch_bounds__(256, 2) attn_prefill_tc_kernel(
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const float inv = 1.0f / l_run;
-            bf16* dst = out + ((size_t)(tok0 + qt * TA_BM + row_t) * H + h) * D;
-            const bf16* grow = (gate != nullptr && row_t < rows) ? gate + (size_t)(tok0 + qt * TA_BM + row_t) * gate_stride + (size_t)h * D : nullptr;
+            bf16* dst = out + ((size_t)(tok0 + qt * TA_BM + row_t) * H + h) * DV;
+            const bf16* grow = (gate != nullptr && row_t < rows) ? gate + (size_t)(tok0 + qt * TA_BM + row_t) * gate_stride + (size_t)h * DV : nullptr;
 #pragma unroll
-            for (int c = 0; c < D / 32; ++c) {
+            for (int c = 0; c < DV / 32; ++c) {
                 float ov[32];
                 tmem_ld32(lane_base + TA_O_COL + c * 32, ov);
                 if (grow != nullptr) {                         // an output gate: times sigmoid(g), element by element
@@ -569,7 +597,7 @@ MB_API int mb_attn_prefill_tc(const void* q, const void* k_cache, const void* v_
     const int box_rows = page_size < TA_BN ? page_size : TA_BN;
     rc = map_2d(&mk, k_cache, cache_rows, D, box_rows);
     if (rc) return rc;
-    rc = map_2d(&mv, v_cache, cache_rows, D, box_rows);
+    rc = TA_V_IN_K ? map_2d(&mv, k_cache, cache_rows, D, box_rows) : map_2d(&mv, v_cache, cache_rows, DV, box_rows);
     if (rc) return rc;
     dim3 grid((max_query_len + TA_BM - 1) / TA_BM, K * GROUP, requests);
     return launch_kernel(attn_prefill_tc_kernel, grid, 256, TA_SMEM, s, 0, mq, mk, mv, (bf16*)out, block_table, max_pages, cu_tokens,

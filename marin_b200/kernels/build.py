@@ -166,6 +166,8 @@ LIBRARIES: Dict[str, List[str]] = {
 #: (head size, query heads per kv head) the fast attention kernels are built for by ``build_all``; any other
 #: layout a model brings is compiled when that model first runs
 ATTENTION_LAYOUTS = [(128, 4), (128, 5), (128, 2), (16, 2), (32, 4), (48, 2)]
+#: (page row, latent width, query heads) of attention over a shared latent the tcgen05 prompt kernel is built for by ``build_all``
+LATENT_LAYOUTS = [(160, 128, 32), (80, 64, 8)]
 
 
 def build_many(jobs: Dict[str, tuple], verbose: bool = True) -> List[str]:
@@ -194,9 +196,16 @@ def attention_job(d: int, group: int) -> tuple:
     return (["attention_fast.cu"], [f"HEAD_DIM={d}", f"GROUP={group}"])
 
 
-def attention_tc_job(d: int, group: int) -> tuple:
-    """Sources and defines of the tensor-core prefill attention kernel for one head layout."""
-    return (["attention_tc.cu"], [f"HEAD_DIM={d}", f"GROUP={group}"])
+def attention_tc_job(d: int, group: int, dv: int = 0, values_in_keys: bool = False) -> tuple:
+    """Sources and defines of the tensor-core prefill attention kernel for one head layout (``values_in_keys``: the
+    values are the first ``dv`` elements of the key rows)."""
+    if not values_in_keys:
+        return (["attention_tc.cu"], [f"HEAD_DIM={d}", f"GROUP={group}"])
+    return (["attention_tc.cu"], [f"HEAD_DIM={d}", f"V_DIM={dv}", f"GROUP={group}", "V_IN_K"])
+
+
+def attention_tc_name(d: int, group: int, dv: int = 0, values_in_keys: bool = False) -> str:
+    return f"mb_attention_tc_d{d}_g{group}" if not values_in_keys else f"mb_attention_tc_d{d}_v{dv}_g{group}_vk"
 
 
 def build_all(verbose: bool = True) -> List[str]:
@@ -207,6 +216,8 @@ def build_all(verbose: bool = True) -> List[str]:
         jobs[f"mb_attention_fast_d{d}_g{g}"] = attention_job(d, g)
         if d in (64, 128):
             jobs[f"mb_attention_tc_d{d}_g{g}"] = attention_tc_job(d, g)
+    for d, dv, g in LATENT_LAYOUTS:
+        jobs[attention_tc_name(d, g, dv, True)] = attention_tc_job(d, g, dv, True)
     return build_many(jobs, verbose)
 
 

@@ -1255,6 +1255,7 @@ def attention_sink(q, k_cache, v_cache, out, ctx, block_table, H: int, K: int, d
     per_row = H * (d + (3 if gate is not None else 2) * dv) * size
     key_bytes = (d if values_in_keys else K * (d + dv)) * size      # what one cached position holds for this layer
     if use_fast_sink_attention and fast_sink_attention_supported(q.dtype, H, K, d, dv, values_in_keys) and page_size & (page_size - 1) == 0:
+        kv_heads = K
         if values_in_keys:
             # one kv head that every query head reads: a CTA takes as many query heads as the kernels group, and `K` counts
             # those groups from here on
@@ -1281,14 +1282,15 @@ def attention_sink(q, k_cache, v_cache, out, ctx, block_table, H: int, K: int, d
         if ctx.num_requests > nd and launch_log is not None:
             _cost((T - nd) * per_row, 0.0, key_bytes, 2.0 * H * (d + dv))
             _pending_cost["rows"] = "prefill"
-        if (ctx.num_requests > nd and use_tc_attention and d == dv and d in (64, 128) and page_size >= 16 and not values_in_keys
+        if (ctx.num_requests > nd and use_tc_attention and tc_sink_attention_supported(d, dv, values_in_keys) and page_size >= 16
                 and (gate is None or (gate.data_ptr() % 16 == 0 and gate_stride % 8 == 0))):
             # heads of 64 or 128 with values as wide: the tcgen05 kernel that plain causal attention uses takes the chunked
-            # mask, the sink and the gate as parameters
-            tc = build.load(f"mb_attention_tc_d{d}_g{H // K}", *build.attention_tc_job(d, H // K))
+            # mask, the sink and the gate as parameters; over a shared latent one CTA per query head reads the one kv head's rows
+            g = H // kv_heads
+            tc = build.load(build.attention_tc_name(d, g, dv, values_in_keys), *build.attention_tc_job(d, g, dv, values_in_keys))
             _check(tc.mb_attn_prefill_tc(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _c_int(max_pages),
                                          _ptr(ctx.cu_tokens), _ptr(ctx.seq_lens), _c_int(nd), _c_int(ctx.num_requests - nd),
-                                         _c_int(ctx.max_query_len), _c_int(T), _c_int(K), _c_int(page_size),
+                                         _c_int(ctx.max_query_len), _c_int(T), _c_int(kv_heads), _c_int(page_size),
                                          ctypes.c_longlong(k_cache.shape[0]), _c_float(scale), _c_int(window),
                                          _ptr(_scratch_for(q.device).error), _c_int(chunk), _c_int(int(sink)), _ptr(gate),
                                          _c_int(gate_stride), _ptr(sink_logits), _stream()), "attention (sink, prefill, tensor cores)")
@@ -1320,6 +1322,14 @@ def sink_group(H: int, K: int, values_in_keys: bool = False) -> int:
     return max(g for g in range(1, 9) if H % g == 0)
 
 
+def tc_sink_attention_supported(d: int, dv: int, values_in_keys: bool = False) -> bool:
+    """Head layouts the tcgen05 prompt kernel is compiled for: keys and values of 64 or of 128; or values that are the
+    first 64 or 128 elements of key rows of 64 to 192 (a multiple of 16)."""
+    if values_in_keys:
+        return dv in (64, 128) and dv <= d <= 192 and d % 16 == 0
+    return d == dv and d in (64, 128)
+
+
 def fast_sink_attention_supported(dtype, H: int, K: int, d: int, dv: int, values_in_keys: bool = False) -> bool:
     """Head sizes in multiples of 16, values up to 128 wide, keys up to 128 (up to 256 where the values are the start of
     the key rows), at most 8 query heads per kv head (any number of heads over a shared latent)."""
@@ -1348,8 +1358,8 @@ def sink_attention_jobs(dtype, H: int, K: int, d: int, dv: int, values_in_keys: 
     if use_fast_sink_attention and fast_sink_attention_supported(dtype, H, K, d, dv, values_in_keys):
         g = sink_group(H, K, values_in_keys)
         jobs[_sink_name(d, dv, g, values_in_keys)] = _sink_job(d, dv, g, values_in_keys)
-        if d == dv and d in (64, 128) and not values_in_keys:
-            jobs[f"mb_attention_tc_d{d}_g{H // K}"] = build.attention_tc_job(d, H // K)
+        if use_tc_attention and tc_sink_attention_supported(d, dv, values_in_keys):
+            jobs[build.attention_tc_name(d, H // K, dv, values_in_keys)] = build.attention_tc_job(d, H // K, dv, values_in_keys)
     return jobs
 
 

@@ -87,8 +87,8 @@ def test_the_schedule_and_the_cache_needs_follow_the_layers():
     needs = model.cache_needs()
     assert needs[0] == PagedKV(1, 64, 70, 64) and needs[3] == PagedKV(2, 32, 16, 48) and needs[2] is None
     # a latent layer keeps one row per position, its values inside it: no value pages
-    assert needs[1] == PagedKV(1, 64, None, 48, values_in_keys=True) and needs[4] == PagedKV(1, 128, None, 112, values_in_keys=True)
-    assert needs[1].bytes_per_token(torch.bfloat16) == 64 * 2
+    assert needs[1] == PagedKV(1, 80, None, 64, values_in_keys=True) and needs[4] == PagedKV(1, 128, None, 112, values_in_keys=True)
+    assert needs[1].bytes_per_token(torch.bfloat16) == 80 * 2
     mix = [b.mixer for b in model.blocks]
     assert mix[0].learned_sink and mix[0].window == 70 and mix[0].position.interleaved and mix[0].qk_norm is None and not mix[0].bias
     assert mix[2].own_latent is False and mix[1].own_latent and "l2.mix.dkv" not in {s.name for s in mix[2].tensor_specs()}
@@ -133,3 +133,20 @@ def test_band_scaled_frequencies(rot):
         assert rot["dims"] < 16 or bool(((ratio < 1.0) & (ratio > 1.0 / rot["scaling"]["factor"] + 1e-9)).any())
     else:
         assert spec.kind == "rope"
+
+
+def test_which_prompt_kernel_a_head_layout_gets():
+    """The tcgen05 prompt kernel takes keys and values of 64 or 128 alike, or page rows of 64 to 192 numbers whose first 64 or
+    128 are the values; a latent layer asks for the kernels of its own layout and a name tells the layouts apart."""
+    from marin_b200.kernels import build, ops
+
+    assert ops.tc_sink_attention_supported(64, 64) and ops.tc_sink_attention_supported(128, 128)
+    assert not ops.tc_sink_attention_supported(128, 64) and not ops.tc_sink_attention_supported(96, 96)
+    for d, dv, ok in ((160, 128, True), (80, 64, True), (192, 128, True), (64, 64, True), (128, 96, False), (208, 128, False),
+                      (72, 64, False), (112, 48, False), (256, 128, False)):
+        assert ops.tc_sink_attention_supported(d, dv, True) == ok, (d, dv)
+    jobs = ops.sink_attention_jobs(torch.bfloat16, 12, 1, 160, 128, values_in_keys=True)
+    assert build.attention_tc_name(160, 12, 128, True) in jobs and jobs[build.attention_tc_name(160, 12, 128, True)][1][-1] == "V_IN_K"
+    assert build.attention_tc_name(128, 4) == "mb_attention_tc_d128_g4" and build.attention_tc_name(128, 4) not in jobs
+    assert not any("attention_tc" in n for n in ops.sink_attention_jobs(torch.bfloat16, 4, 1, 128, 96, values_in_keys=True))
+    assert not any("attention_tc" in n for n in ops.sink_attention_jobs(torch.float32, 12, 1, 160, 128, values_in_keys=True))

@@ -287,6 +287,8 @@ def plain_latent(x, w, m, kept=None, eps=1e-5):
     {"heads": 4, "dim": 16, "rot_dim": 16, "vdim": 24, "kv_rank": 112, "scale": 0.18, "rot": {"base": 30000.0, "dims": 16}},
     {"heads": 2, "dim": 64, "rot_dim": 32, "vdim": 128, "kv_rank": 128, "scale": 0.1, "rot": {"base": 1000.0, "dims": 32}},
     {"heads": 10, "dim": 16, "rot_dim": 16, "vdim": 16, "kv_rank": 32, "scale": 0.2},
+    {"heads": 3, "dim": 32, "rot_dim": 16, "vdim": 32, "kv_rank": 64, "scale": 0.12, "rot": {"base": 500.0, "dims": 16}},
+    {"heads": 2, "dim": 32, "rot_dim": 64, "vdim": 64, "kv_rank": 128, "scale": 0.09, "rot": {"base": 10000.0, "dims": 64}},
     {"heads": 1, "dim": 8, "rot_dim": 8, "vdim": 8, "kv_rank": 24, "scale": 0.3, "rot": {"base": 10.0, "dims": 4}},
 ], ids=lambda m: f"{m['heads']}x{m['dim']}+{m['rot_dim']}x{m['vdim']}r{m['kv_rank']}")
 def test_latent_attention_alone_and_read_by_a_second_layer(dtype, m):
@@ -311,21 +313,22 @@ def test_latent_attention_alone_and_read_by_a_second_layer(dtype, m):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_one_far_latent_stands_out_among_hundreds(dtype):
+@pytest.mark.parametrize("rank", [32, 64])
+def test_one_far_latent_stands_out_among_hundreds(dtype, rank):
     """Every head's rotated query part and the shared key part come from the same matrix, read the first half of the input
     only and are not rotated; the row at position 5 repeats the last row's first half, longer, with a second half of its own
     (so its latent, and with it its value, differs).  Its key then scores far above the rest for the last query, 700
     positions later."""
     rt = runtime(dtype)
     T, hidden = 700, 32
-    m = {"heads": 2, "dim": 16, "rot_dim": 16, "vdim": 24, "kv_rank": 32, "scale": 0.3}
+    m = {"heads": 2, "dim": 16, "rot_dim": 16, "vdim": 24, "kv_rank": rank, "scale": 0.3}
     w = latent_weights(hidden, m, 9)
     q = w["m.q"].float().view(2, 32, hidden)
     q[0, 16:, 16:] = 0.0
     q[1, 16:] = q[0, 16:]
     w["m.q"] = bf(q.reshape(64, hidden))
     dkv = w["m.dkv"].float()
-    dkv[32:] = q[0, 16:]
+    dkv[rank:] = q[0, 16:]
     w["m.dkv"] = bf(dkv)
     w["m.uk"] = bf(0.2 * w["m.uk"].float())                 # the unrotated part stays small beside the shared part
     g = torch.Generator().manual_seed(10)
