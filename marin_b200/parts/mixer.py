@@ -556,7 +556,7 @@ class LatentAttention(Mixer):
         ops.stage_name = "q into the latent"
         ops.heads_product(rows, self.q_head, dn, self.w_uk_t, q, D)
         mixed = ws.get("latent_out", (T, H * r), x.dtype)
-        ops.stage_name = "attention"
+        ops.stage_name = "attention, latent"
         plans = ctx.decode_plans
         ops.attention_sink(q, cache.k, cache.k, mixed, ctx, cache.block_table, H, 1, D, r, self.scale, 0, 0, self.sink, None,
                            plans.get(self.decode_plan_key()) if plans else None, self.sink_logits)
