@@ -409,8 +409,10 @@ def arch_mode(args, pk, arch: str) -> int:
         clock_record = clocks.stop()
         # a layer that keeps a state reads the same bytes whatever the context; a layer that keeps keys reads them all
         state_bytes = sum(n.bytes() for n in engine.cache.state_needs.values())
-        paged_tok = sum(len(g.entries) * g.need.bytes_per_token(engine.rt.dtype) for g in engine.cache.groups)
-        step_bytes = weight_bytes + args.batch * (run["mean_context"] * paged_tok + 2 * state_bytes)
+        # (a layer with a window reads the window's positions, however long the sequence)
+        paged = sum(len(g.entries) * g.need.bytes_per_token(engine.rt.dtype) * min(run["mean_context"], g.need.window or run["mean_context"])
+                    for g in engine.cache.groups)
+        step_bytes = weight_bytes + args.batch * (paged + 2 * state_bytes)
         achieved = step_bytes / (run["ms_per_step"] / 1e3) / 1e9
         out[name] = {
             "decode_tok_s": round(run["tok_s"], 1), "decode_ms_per_step": round(run["ms_per_step"], 4), "decode_launches": run["launches"],

@@ -31,7 +31,7 @@
 #endif
 static_assert(HEAD_DIM % 16 == 0 && HEAD_DIM >= 16 && HEAD_DIM <= 256, "key heads: a multiple of 16 up to 256");
 static_assert(V_DIM % 16 == 0 && V_DIM >= 16 && V_DIM <= 128, "value heads: a multiple of 16 up to 128");
-static_assert(GROUP >= 1 && GROUP <= 8, "1 to 8 query heads per kv head");
+static_assert(GROUP >= 1 && GROUP <= 16, "1 to 16 query heads per kv head");
 
 #define D HEAD_DIM
 #define DV V_DIM
@@ -62,6 +62,9 @@ __device__ __forceinline__ int first_seen(int pos, int window, int chunk) {
 }
 
 // The rows of one 64-key block of K and V (cp.async); keys outside [k_first, k_last] are zero (their pages may not exist).
+// Two threads a row (128 threads, 64 rows), each taking every other 16-byte piece: the page look-up and the row's address
+// are worked out once a thread and block, and the copies that follow differ by constants.  (With one piece a thread and
+// turn, index arithmetic and look-ups were most of the kernel's instructions: 800 a warp and block, against 36 MMAs.)
 __device__ __forceinline__ void load_kv_block(bf16* dst_k, bf16* dst_v, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                                               const int* __restrict__ table, int K, int kh, int page_shift, int key0, int k_first, int k_last) {
 #ifdef V_IN_K
@@ -69,24 +72,35 @@ __device__ __forceinline__ void load_kv_block(bf16* dst_k, bf16* dst_v, const bf
 #else
     constexpr int CK = D / 8, CV = DV / 8;
 #endif
-    const int page_mask = (1 << page_shift) - 1;
-    for (int idx = threadIdx.x; idx < BN * (CK + CV); idx += 128) {
-        const int row = idx / (CK + CV), c = idx % (CK + CV);
-        const int key = key0 + row;
-        const bool is_k = c < CK;
-        bf16* dst = is_k ? dst_k + row * LDK + c * 8 : dst_v + row * LDV + (c - CK) * 8;
-        if (key <= k_last && key >= k_first) {
+    const int row = threadIdx.x >> 1, half = threadIdx.x & 1;
+    const int key = key0 + row;
+    bf16* dk = dst_k + row * LDK;
+    bf16* dv = dst_v + row * LDV;
+    if (key <= k_last && key >= k_first) {
+        const int page_mask = (1 << page_shift) - 1;
 #ifdef V_IN_K
-            const size_t slot = ((size_t)table[key >> page_shift] << page_shift) + (size_t)(key & page_mask);       // one kv head
+        const size_t slot = ((size_t)table[key >> page_shift] << page_shift) + (size_t)(key & page_mask);       // one kv head
 #else
-            const size_t slot = (((size_t)table[key >> page_shift] * K + kh) << page_shift) + (size_t)(key & page_mask);
+        const size_t slot = (((size_t)table[key >> page_shift] * K + kh) << page_shift) + (size_t)(key & page_mask);
 #endif
-            cp_async16(dst, is_k ? k_cache + slot * D + c * 8 : v_cache + slot * DV + (c - CK) * 8);
-        } else {
-            *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+        const bf16* sk = k_cache + slot * D;
+#pragma unroll
+        for (int c = half; c < CK; c += 2) cp_async16(dk + c * 8, sk + c * 8);
+        if (CV > 0) {
+            const bf16* sv = v_cache + slot * DV;
+#pragma unroll
+            for (int c = half; c < CV; c += 2) cp_async16(dv + c * 8, sv + c * 8);
+        }
+    } else {
+#pragma unroll
+        for (int c = half; c < CK; c += 2) *reinterpret_cast<uint4*>(dk + c * 8) = make_uint4(0, 0, 0, 0);
+        if (CV > 0) {
+#pragma unroll
+            for (int c = half; c < CV; c += 2) *reinterpret_cast<uint4*>(dv + c * 8) = make_uint4(0, 0, 0, 0);
         }
     }
 }
+static_assert(BN == 64, "load_kv_block: two of the 128 threads a row");
 
 #define PF_SMEM ((BM * LDK + BN * LDK + V_ROWS * LDV) * 2)
 
@@ -252,27 +266,34 @@ __global__ void __launch_bounds__(128, 2) attn_sink_prefill_kernel(
 
 // ---- single tokens: the visible keys of a sequence split over CTAs -------------------------------------------------------
 // CTA (chunk, kv head, request): keys [start + chunk * split, + split) where start = lo(pos) rounded down to a block of 64; the
-// GROUP query heads of the kv head are rows 0..GROUP-1 of a 16-row tile; warp w takes keys 16 w .. 16 w + 15 of every block
-// with a running (max, sum) of its own.  The four warps are merged in shared memory in warp order and written as the chunk's
+// GROUP query heads of the kv head are rows 0..GROUP-1 of a 16-row tile (a thread holds row g of the tile's upper half and,
+// with more than 8 heads, row g + 8 of the lower: two running maxima and sums); warp w takes keys 16 w .. 16 w + 15 of every
+// block with a running (max, sum) of its own.  The four warps are merged in shared memory in warp order and written as the chunk's
 // part: acc[chunk][request][head][DV] and ml[chunk][request][head][2] (max in log2 units, sum), float32.
-#define DEC_SMEM ((16 * LDK + BN * LDK + V_ROWS * LDV) * 2)
-static_assert(4 * GROUP * DV * 4 <= BN * LDK * 2 + V_ROWS * LDV * 2, "the warps' sums are written over the key and value block");
+// Rows that are keys and values both are fetched a block ahead, into the other of two buffers: a block of many heads over
+// one row takes about as long to compute as to fetch, and two buffers of rows still leave room for four CTAs an SM.  Keys
+// and values of their own keep one buffer (two halved the CTAs per SM and were slower: 36.8 -> 45.0 us a call at batch 8).
+#ifdef V_IN_K
+#define DEC_STAGES 2
+#else
+#define DEC_STAGES 1
+#endif
+#define DEC_STAGE_ELEMS (BN * LDK + V_ROWS * LDV)
+#define DEC_KV_BYTES (DEC_STAGES * DEC_STAGE_ELEMS * 2)
+#define DEC_SUM_BYTES (4 * GROUP * DV * 4)                 // the warps' sums are written over the key and value block
+#define DEC_SMEM (16 * LDK * 2 + (DEC_KV_BYTES > DEC_SUM_BYTES ? DEC_KV_BYTES : DEC_SUM_BYTES))
+#define DEC_LOWER (GROUP > 8)                              // the tile's rows 8..15 hold query heads too
 
-__global__ void __launch_bounds__(128) attn_sink_decode_kernel(
+__global__ void __launch_bounds__(128, 4) attn_sink_decode_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache, float* __restrict__ part_acc,
     float* __restrict__ part_ml, const int* __restrict__ block_table, int max_pages, const int* __restrict__ seq_lens, int K,
     int page_shift, float scale, int window, int chunk_size, int split) {
     PDL_ENTER();
     q = pdl_fresh(q); k_cache = pdl_fresh(k_cache); v_cache = pdl_fresh(v_cache);
     extern __shared__ __align__(16) uint8_t smem_raw[];
-    __shared__ float s_m[4][8], s_l[4][8];
+    __shared__ float s_m[4][16], s_l[4][16];
     bf16* sQ = reinterpret_cast<bf16*>(smem_raw);
-    bf16* sK = sQ + 16 * LDK;
-#ifdef V_IN_K
-    bf16* sV = sK;
-#else
-    bf16* sV = sK + BN * LDK;
-#endif
+    bf16* sK0 = sQ + 16 * LDK;
     const int chunk = blockIdx.x, kh = blockIdx.y, r = blockIdx.z, R = gridDim.z;
     const int H = K * GROUP;
     const int len = seq_lens[r], pos = len - 1;
@@ -298,10 +319,30 @@ __global__ void __launch_bounds__(128) attn_sink_decode_kernel(
     const int g = lane >> 2;                                   // this thread's row of the tile: a query head if g < GROUP
     const float sl2 = scale * LOG2E;
     float m_run = -INFINITY, l_run = 0.0f;
+    float m_low = -INFINITY, l_low = 0.0f;                    // row g + 8 (used with more than 8 heads)
+#ifdef V_IN_K
+    load_kv_block(sK0, sK0, k_cache, v_cache, table, K, kh, page_shift, c_begin, lo, pos);
+    cp_async_commit();
+    int stage = 0;
+#endif
     for (int key0 = c_begin; key0 < c_end; key0 += BN) {
+#ifdef V_IN_K
+        bf16* sK = sK0 + stage * DEC_STAGE_ELEMS;
+        bf16* sV = sK;
+        if (key0 + BN < c_end) {                               // the next block, into the buffer the last block's products have left
+            bf16* next = sK0 + (stage ^ 1) * DEC_STAGE_ELEMS;
+            load_kv_block(next, next, k_cache, v_cache, table, K, kh, page_shift, key0 + BN, lo, pos);
+        }
+        cp_async_commit();
+        cp_async_wait<1>();                                    // all but the newest group: this block (and the queries) are here
+        stage ^= 1;
+#else
+        bf16* sK = sK0;
+        bf16* sV = sK + BN * LDK;
         load_kv_block(sK, sV, k_cache, v_cache, table, K, kh, page_shift, key0, lo, pos);
         cp_async_commit();
         cp_async_wait<0>();
+#endif
         __syncthreads();
         float s[2][4];
         s[0][0] = s[0][1] = s[0][2] = s[0][3] = s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.0f;
@@ -314,14 +355,19 @@ __global__ void __launch_bounds__(128) attn_sink_decode_kernel(
             mma_bf16_16816(s[0], qa, b0, b1);
             mma_bf16_16816(s[1], qa, b2, b3);
         }
-        float mx = -INFINITY;
+        float mx = -INFINITY, mx_low = -INFINITY;
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {                      // elements 2 and 3 belong to rows 8..15: no query head
+            for (int e = 0; e < 2; ++e) {                      // elements 2 and 3 belong to rows 8..15
                 const int key = key0 + warp * 16 + j * 8 + 2 * (lane & 3) + e;
-                s[j][e] = (key <= pos && key >= lo) ? s[j][e] * sl2 : -INFINITY;
+                const bool seen = key <= pos && key >= lo;
+                s[j][e] = seen ? s[j][e] * sl2 : -INFINITY;
                 mx = fmaxf(mx, s[j][e]);
+                if (DEC_LOWER) {
+                    s[j][2 + e] = seen ? s[j][2 + e] * sl2 : -INFINITY;
+                    mx_low = fmaxf(mx_low, s[j][2 + e]);
+                }
             }
         }
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
@@ -338,17 +384,37 @@ __global__ void __launch_bounds__(128) attn_sink_decode_kernel(
             sum += s[j][0] + s[j][1];
         }
         l_run = l_run * corr + sum;
+        float corr_low = 1.0f;
         uint32_t pa[4];
         pa[0] = pack_bf16(s[0][0], s[0][1]);
         pa[1] = 0u;
         pa[2] = pack_bf16(s[1][0], s[1][1]);
         pa[3] = 0u;
+        if (DEC_LOWER) {
+            mx_low = fmaxf(mx_low, __shfl_xor_sync(0xffffffffu, mx_low, 1));
+            mx_low = fmaxf(mx_low, __shfl_xor_sync(0xffffffffu, mx_low, 2));
+            const float m_new_low = fmaxf(m_low, mx_low);
+            const float base_low = m_new_low == -INFINITY ? 0.0f : m_new_low;
+            corr_low = ex2_approx(m_low - base_low);
+            m_low = m_new_low;
+            float sum_low = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                s[j][2] = ex2_approx(s[j][2] - base_low);
+                s[j][3] = ex2_approx(s[j][3] - base_low);
+                sum_low += s[j][2] + s[j][3];
+            }
+            l_low = l_low * corr_low + sum_low;
+            pa[1] = pack_bf16(s[0][2], s[0][3]);
+            pa[3] = pack_bf16(s[1][2], s[1][3]);
+        }
         const uint32_t v_addr = (uint32_t)__cvta_generic_to_shared(sV + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDV + (lane >> 4) * 8);
 #pragma unroll
         for (int dt = 0; dt < DV / 8; dt += 2) {
             uint32_t b0, b1, b2, b3;
             ldsm_x4_trans(v_addr + (uint32_t)(dt * 16), b0, b1, b2, b3);
             o[dt][0] *= corr; o[dt][1] *= corr; o[dt + 1][0] *= corr; o[dt + 1][1] *= corr;
+            if (DEC_LOWER) { o[dt][2] *= corr_low; o[dt][3] *= corr_low; o[dt + 1][2] *= corr_low; o[dt + 1][3] *= corr_low; }
             mma_bf16_16816(o[dt], pa, b0, b1);
             mma_bf16_16816(o[dt + 1], pa, b2, b3);
         }
@@ -356,7 +422,12 @@ __global__ void __launch_bounds__(128) attn_sink_decode_kernel(
     }
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
-    float* sums = reinterpret_cast<float*>(sK);               // [4 warps][GROUP][DV]
+    if (DEC_LOWER) {
+        l_low += __shfl_xor_sync(0xffffffffu, l_low, 1);
+        l_low += __shfl_xor_sync(0xffffffffu, l_low, 2);
+    }
+    cp_async_wait<0>();
+    float* sums = reinterpret_cast<float*>(sK0);              // [4 warps][GROUP][DV]
     if (g < GROUP) {
         const int col = 2 * (lane & 3);
 #pragma unroll
@@ -365,6 +436,15 @@ __global__ void __launch_bounds__(128) attn_sink_decode_kernel(
             sums[(warp * GROUP + g) * DV + i * 8 + col + 1] = o[i][1];
         }
         if ((lane & 3) == 0) { s_m[warp][g] = m_run; s_l[warp][g] = l_run; }
+    }
+    if (DEC_LOWER && g + 8 < GROUP) {
+        const int col = 2 * (lane & 3);
+#pragma unroll
+        for (int i = 0; i < DV / 8; ++i) {
+            sums[(warp * GROUP + g + 8) * DV + i * 8 + col] = o[i][2];
+            sums[(warp * GROUP + g + 8) * DV + i * 8 + col + 1] = o[i][3];
+        }
+        if ((lane & 3) == 0) { s_m[warp][g + 8] = m_low; s_l[warp][g + 8] = l_low; }
     }
     __syncthreads();
     const size_t at = ((size_t)chunk * R + r) * H + (size_t)kh * GROUP;

@@ -41,12 +41,17 @@ class StageRow:
         return self.flops / (self.share_us * 1e-6) / 1e12 if self.share_us > 0 else 0.0
 
 
-def lengths_of(runner: Runner, entries: Sequence[StepEntry]):
-    """Keys read and (query, key) pairs of the single-token rows and of the portions of a step that is about to run."""
+def lengths_of(runner: Runner, entries: Sequence[StepEntry], window: int = 0):
+    """Keys read and (query, key) pairs of the single-token rows and of the portions of a step that is about to run; a
+    position sees the last ``window`` keys only (0: all before it)."""
     counts = {"decode": [0, 0], "prefill": [0, 0]}
     for e in entries:
         before, n = runner.length(e.req_id), len(e.tokens)
         which = counts["decode" if n == 1 else "prefill"]
+        if window > 0:
+            which[0] += min(before + n, window - 1 + n)
+            which[1] += sum(min(i + 1, window) for i in range(before, before + n))
+            continue
         which[0] += before + n
         which[1] += n * before + n * (n + 1) // 2
     total = [counts["decode"][0] + counts["prefill"][0], counts["decode"][1] + counts["prefill"][1]]
@@ -70,7 +75,10 @@ def profile_steps(runner: Runner, make_entries: Callable[[int], Sequence[StepEnt
 
     def one(i, log=None):
         entries = make_entries(i)
-        sizes = lengths_of(runner, entries)
+        # (per window an attention kernel named in its launch record; 0: every earlier key is seen)
+        sizes = {0: lengths_of(runner, entries)}
+        for w in sorted({int(getattr(b.mixer, "window", 0) or 0) for b in getattr(runner.model, "blocks", [])} - {0}):
+            sizes[w] = lengths_of(runner, entries, w)
         ops.launch_log = log
         try:
             logits = runner.step(entries)
@@ -119,7 +127,8 @@ def profile_steps(runner: Runner, make_entries: Callable[[int], Sequence[StepEnt
     if gaps:
         rows.append(StageRow("(between steps)", "the device idle: host work, launch", 0, statistics.median(gaps), 0.0, 0.0, 0.0))
     for k, entry in enumerate(labels):
-        keys, pairs = sizes.get(entry.get("rows", "all"), sizes["all"])
+        seen = sizes.get(int(entry.get("window", 0)), sizes[0])
+        keys, pairs = seen.get(entry.get("rows", "all"), seen["all"])
         nbytes = entry["bytes"] + entry["bytes_per_key"] * keys
         flops = entry["flops"] + entry["flops_per_pair"] * pairs
         key = (entry["stage"], entry["kernel"])

@@ -9,6 +9,7 @@ crates/cuda/src/ops.rs:53-236.)
 from __future__ import annotations
 
 import ctypes
+import functools
 import os
 import weakref
 from typing import Optional
@@ -1270,7 +1271,7 @@ def attention_sink(q, k_cache, v_cache, out, ctx, block_table, H: int, K: int, d
             ml = ctx.workspace.get("sink_part_sums", (plan.chunks, nd, H, 2), torch.float32)
             if launch_log is not None:
                 _cost(nd * per_row + 2 * _size(acc), 0.0, key_bytes, 2.0 * H * (d + dv))
-                _pending_cost["rows"] = "decode"
+                _pending_cost["rows"], _pending_cost["window"] = "decode", window
             _check(lib.mb_attn_sink_decode(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(acc), _ptr(ml), _ptr(block_table),
                                            _c_int(max_pages), _ptr(ctx.seq_lens), _c_int(nd), _c_int(K), _c_int(page_size), _c_float(scale),
                                            _c_int(window), _c_int(chunk), _c_int(plan.split), _c_int(plan.chunks), _stream()),
@@ -1281,7 +1282,7 @@ def attention_sink(q, k_cache, v_cache, out, ctx, block_table, H: int, K: int, d
                                           _stream()), "attention (sink, parts merged)")
         if ctx.num_requests > nd and launch_log is not None:
             _cost((T - nd) * per_row, 0.0, key_bytes, 2.0 * H * (d + dv))
-            _pending_cost["rows"] = "prefill"
+            _pending_cost["rows"], _pending_cost["window"] = "prefill", window
         if (ctx.num_requests > nd and use_tc_attention and tc_sink_attention_supported(d, dv, values_in_keys) and page_size >= 16
                 and (gate is None or (gate.data_ptr() % 16 == 0 and gate_stride % 8 == 0))):
             # heads of 64 or 128 with values as wide: the tcgen05 kernel that plain causal attention uses takes the chunked
@@ -1303,7 +1304,7 @@ def attention_sink(q, k_cache, v_cache, out, ctx, block_table, H: int, K: int, d
         return
     if launch_log is not None:
         _cost(T * per_row, 0.0, key_bytes, 2.0 * H * (d + dv))
-        _pending_cost["rows"] = "all"
+        _pending_cost["rows"], _pending_cost["window"] = "all", window
     _check(_lib("mb_attention_sink").mb_attention_sink(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _code(q), _ptr(block_table), _c_int(block_table.shape[1]), _ptr(ctx.req_index),
         _ptr(ctx.positions), _c_int(T), _c_int(H), _c_int(K), _c_int(d), _c_int(dv), _c_int(page_size), _c_float(scale), _c_int(window),
@@ -1314,12 +1315,16 @@ def attention_sink(q, k_cache, v_cache, out, ctx, block_table, H: int, K: int, d
 use_fast_sink_attention = True
 
 
+#: query heads a CTA of the single-token kernel can take: the 16 rows of an mma tile
+SINK_GROUP_MAX = 16
+
+
 def sink_group(H: int, K: int, values_in_keys: bool = False) -> int:
-    """Query heads a CTA of the tensor-core kernels takes together: those of one kv head; where every query head reads the
-    same page rows (a shared latent: one kv head), the largest divisor of the head count up to 8."""
+    """Query heads a CTA of the tensor-core kernels takes together (the rows of one 16-row tile): those of one kv head; where
+    every query head reads the same page rows (a shared latent: one kv head), the largest divisor of the head count up to 16."""
     if not values_in_keys:
         return H // K
-    return max(g for g in range(1, 9) if H % g == 0)
+    return max(g for g in range(1, SINK_GROUP_MAX + 1) if H % g == 0)
 
 
 def tc_sink_attention_supported(d: int, dv: int, values_in_keys: bool = False) -> bool:
@@ -1332,11 +1337,11 @@ def tc_sink_attention_supported(d: int, dv: int, values_in_keys: bool = False) -
 
 def fast_sink_attention_supported(dtype, H: int, K: int, d: int, dv: int, values_in_keys: bool = False) -> bool:
     """Head sizes in multiples of 16, values up to 128 wide, keys up to 128 (up to 256 where the values are the start of
-    the key rows), at most 8 query heads per kv head (any number of heads over a shared latent)."""
+    the key rows), at most 16 query heads per kv head (any number of heads over a shared latent)."""
     if values_in_keys and K != 1:
         return False
     return (dtype == torch.bfloat16 and d % 16 == 0 and dv % 16 == 0 and 16 <= d <= (256 if values_in_keys else 128) and 16 <= dv <= 128
-            and H % K == 0 and 1 <= sink_group(H, K, values_in_keys) <= 8 and (not values_in_keys or dv <= d))
+            and H % K == 0 and 1 <= sink_group(H, K, values_in_keys) <= SINK_GROUP_MAX and (not values_in_keys or dv <= d))
 
 
 def _sink_job(d: int, dv: int, group: int, values_in_keys: bool = False) -> tuple:
@@ -1363,9 +1368,8 @@ def sink_attention_jobs(dtype, H: int, K: int, d: int, dv: int, values_in_keys: 
     return jobs
 
 
-#: CTAs per SM the single tokens' keys are split into (a CTA walks its keys one 64-key block at a time and waits for each:
-#: it is the number of CTAs in flight that hides the latency)
-#: (8, 16 and 32 were measured at batch 8 and a context of 4,096: 36.6 us a call with 4, then 37.1, 40.7, 44.9.)
+#: CTAs of the single-token kernel that an SM holds at a time (its launch bounds promise as many; a CTA walks its keys one
+#: 64-key block at a time and waits for each: it is the number of CTAs in flight that hides the latency)
 SINK_DECODE_CTAS_PER_SM = int(os.environ.get("MARIN_B200_SINK_CTAS", "4"))
 SINK_DECODE_LEAST_SPLIT = 128
 
@@ -1381,9 +1385,14 @@ class SinkDecodePlan:
 
 def sink_decode_plan(dtype, requests: int, H: int, K: int, d: int, dv: int, span: int, window: int, chunk: int,
                      values_in_keys: bool = False):
-    """Enough chunks for about four CTAs per SM over all requests and kv heads, none shorter than 64 keys.  A token sees at
-    most its window or its chunk of keys, whatever the sequence's length: the split follows that, not the context.  None
-    where the plain kernel runs (it needs no plan)."""
+    """The number of chunks whose CTAs finish soonest: the CTAs of all requests, kv heads and chunks run in waves of as many as
+    the device holds at a time, and a wave lasts as long as one CTA's walk over its chunk, so the cost of ``c`` chunks is
+    ``waves(c) * (blocks per chunk + a CTA's start and end)``; among equals, the fewest chunks (the merge reads them all).  A
+    chunk is a multiple of 64 keys, two blocks at least where there are that many (with one request the merge of 74
+    one-block chunks took twice as long as the attention itself).  A token sees at most its window or its chunk of keys,
+    whatever the sequence's length: the split follows that, not the context.  None where the plain kernel runs (it needs no
+    plan).  (Filling "about four CTAs per SM" rounded up instead left a second wave of a few CTAs, which doubled the call:
+    640 CTAs over 592 places took 70 us at batch 64 over a shared latent, where one CTA's walk takes 35.)"""
     if not (use_fast_sink_attention and fast_sink_attention_supported(dtype, H, K, d, dv, values_in_keys)):
         return None
     K = H // sink_group(H, K, values_in_keys)          # CTAs per request and chunk
@@ -1393,12 +1402,23 @@ def sink_decode_plan(dtype, requests: int, H: int, K: int, d: int, dv: int, span
     if chunk > 0:
         seen = min(seen, chunk)
     longest = seen + 63                                # the first chunk starts on a block border at or before the first seen key
-    want = max(1, -(-SINK_DECODE_CTAS_PER_SM * SM_COUNT // max(1, requests * K)))
-    # (two key blocks per chunk at least where there are that many: with one request the merge of 74 one-block chunks took
-    # twice as long as the attention itself: 87 + 175 us over 12 layers against 101 + 75 with 33 chunks)
-    least = SINK_DECODE_LEAST_SPLIT if longest > SINK_DECODE_LEAST_SPLIT else 64
-    split = max(least, -(-(-(-longest // want)) // 64) * 64)
+    split = _sink_split(max(1, requests * K), longest, max(1, SINK_DECODE_CTAS_PER_SM * SM_COUNT))
     return SinkDecodePlan(split, max(1, -(-longest // split)))
+
+
+@functools.lru_cache(maxsize=4096)
+def _sink_split(per_chunk: int, longest: int, places: int) -> int:
+    """Keys per chunk (see :func:`sink_decode_plan`): ``per_chunk`` CTAs a chunk, ``places`` CTAs on the device at a time."""
+    blocks = -(-longest // 64)
+    least = SINK_DECODE_LEAST_SPLIT // 64 if longest > SINK_DECODE_LEAST_SPLIT else 1
+    best = None
+    for c in range(1, min(1024, max(1, -(-blocks // least))) + 1):          # (the merge kernel takes up to 1,024 chunks)
+        per = -(-blocks // c)
+        waves = -(-c * per_chunk // places)
+        cost = waves * (per + 1.5)                     # a CTA's start (its queries) and end (its part written) beside its blocks
+        if best is None or cost < best[0] - 1e-9:
+            best = (cost, per)
+    return best[1] * 64
 
 
 # ---- attention over a latent that keys and values share (csrc/attention_latent.cu) -------------------------------------------

@@ -407,6 +407,11 @@ class SinkAttention(Mixer):
         self.rt = rt
 
     def flops(self, tokens: int, pairs: int = 0) -> float:
+        w = self.window
+        if w and tokens > w and pairs == tokens * (tokens + 1) // 2:
+            pairs = w * (w + 1) // 2 + (tokens - w) * w          # one prompt from its first position: the window's pairs
+        elif w:
+            pairs = min(pairs, tokens * w)
         return super().flops(tokens, pairs) + 2.0 * pairs * self.heads * (self.head_dim + self.v_head_dim)
 
     def kernel_jobs(self, dtype) -> Dict[str, tuple]:

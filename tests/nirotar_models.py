@@ -54,7 +54,7 @@ CONFIG_A = {
 # Sizes the tensor-core kernels are made for: heads of 64 with values as wide and pages of 16 (prompt portions on the tcgen05
 # kernel), page rows of 80 numbers (a latent of 64, whose prompt portions run on the tcgen05 kernel too, the second 64-column
 # panel of a row partly filled) and of 128 in two latent groups of different sizes, a window that is no multiple of anything
-# and one of exactly a page, experts in whole steps of 64.
+# and one of exactly a page, experts in whole steps of 64; sixteen latent heads (a full tile of the single-token kernel).
 BANDS_B = {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 64}
 CONFIG_B = {
     "architecture": "Nirotar", "vocab": 160, "width": 128, "norm": {"eps": 1e-6},
@@ -63,12 +63,12 @@ CONFIG_B = {
         {"type": "latent_attention", "mixer": _latent(8, 32, 16, 32, 64, 0.15, rot={"base": 1000.0, "dims": 16}), "mlp": _moe(128, 4, 1, shared=64)},
         {"type": "latent_attention", "mixer": _latent(2, 64, 16, 64, 64, 0.11, rot={"base": 1000.0, "dims": 16}, kv_from=1), "mlp": None},
         {"type": "attention", "mixer": _attn(6, 2, 32, 48, 0.2, mask=16, rot={"base": 500.0, "dims": 16}), "mlp": _moe(64, 6, 3)},
-        {"type": "latent_attention", "mixer": _latent(4, 16, 16, 16, 112, 0.18, rot={"base": 30000.0, "dims": 16}), "mlp": _moe(64, 8, 2, shared=64)},
+        {"type": "latent_attention", "mixer": _latent(16, 16, 16, 16, 112, 0.18, rot={"base": 30000.0, "dims": 16}), "mlp": _moe(64, 8, 2, shared=64)},
     ],
 }
 # Edges of the parameter space: a window of one position (a token sees itself and the sink), a window longer than any
-# sequence, as many kv heads as heads, ten latent heads on one page row (more than the tensor-core kernel groups), a rotated
-# part that is not rotated at all, two experts that are both always chosen.
+# sequence, as many kv heads as heads, ten latent heads on one page row (the lower half of the single-token kernel's tile
+# partly filled), a rotated part that is not rotated at all, two experts that are both always chosen.
 CONFIG_C = {
     "architecture": "Nirotar", "vocab": 70, "width": 64, "norm": {"eps": 1e-6},
     "layers": [

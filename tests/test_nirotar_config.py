@@ -150,3 +150,25 @@ def test_which_prompt_kernel_a_head_layout_gets():
     assert build.attention_tc_name(128, 4) == "mb_attention_tc_d128_g4" and build.attention_tc_name(128, 4) not in jobs
     assert not any("attention_tc" in n for n in ops.sink_attention_jobs(torch.bfloat16, 4, 1, 128, 96, values_in_keys=True))
     assert not any("attention_tc" in n for n in ops.sink_attention_jobs(torch.float32, 12, 1, 160, 128, values_in_keys=True))
+
+
+def test_single_token_attention_is_split_into_whole_waves():
+    """The chunks cover every key a token sees, a chunk is a multiple of 64 keys, and the CTAs of all chunks never leave a
+    few for a wave of their own when fewer chunks fill one wave."""
+    from marin_b200.kernels import ops
+
+    places = ops.SINK_DECODE_CTAS_PER_SM * ops.SM_COUNT
+    for requests, H, K, d, dv, span, window, shared in [(64, 32, 1, 160, 128, 4160, 0, True), (8, 32, 1, 160, 128, 4160, 0, True),
+                                                       (8, 32, 8, 128, 128, 4160, 0, False), (1, 32, 8, 128, 128, 70000, 0, False),
+                                                       (3, 12, 1, 32, 32, 500, 40, False), (64, 32, 8, 128, 128, 4160, 1024, False),
+                                                       (2, 4, 2, 64, 64, 20, 0, False), (5, 6, 2, 64, 64, 129, 0, False)]:
+        plan = ops.sink_decode_plan(torch.bfloat16, requests, H, K, d, dv, span, window, 0, shared)
+        seen = min(span, window) if window else span
+        assert plan.split % 64 == 0 and plan.split * plan.chunks >= seen + 63 and plan.split * (plan.chunks - 1) < seen + 63
+        assert plan.chunks <= 1024 and (plan.split >= 128 or seen + 63 <= 128)
+        ctas = requests * (H // ops.sink_group(H, K, shared)) * plan.chunks
+        per_chunk = ctas // plan.chunks
+        # more than a wave only if one chunk's CTAs alone exceed it, or the waves are full ones
+        assert ctas <= places or per_chunk > places or ctas % places == 0 or plan.chunks == 1 or ctas / places > 1.5, (requests, H, K, plan.chunks)
+    assert ops.sink_decode_plan(torch.bfloat16, 64, 32, 1, 160, 128, 4160, 0, 0, True).chunks == 4      # 512 CTAs in one wave, not 640 in two
+    assert ops.sink_decode_plan(torch.float32, 8, 32, 8, 128, 128, 4160, 0, 0) is None                  # the plain kernel needs no plan

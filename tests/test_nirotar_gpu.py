@@ -141,6 +141,9 @@ BANDS = {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 32}
     {"heads": 2, "kv_heads": 1, "dim": 80, "vdim": 48, "scale": 0.11, "rot": {"base": 100.0, "dims": 80, "scaling": BANDS}},
     {"heads": 5, "kv_heads": 1, "dim": 24, "vdim": 40, "scale": 0.25, "mask": {"size": 64}, "rot": {"base": 100.0, "dims": 2}},
     {"heads": 2, "kv_heads": 2, "dim": 64, "vdim": 64, "scale": 0.125},
+    # more than 8 query heads a kv head: both halves of the single-token kernel's 16-row tile, the lower one partly filled
+    {"heads": 12, "kv_heads": 1, "dim": 32, "vdim": 32, "scale": 0.18, "mask": {"size": 40}, "rot": {"base": 100.0, "dims": 16}},
+    {"heads": 32, "kv_heads": 2, "dim": 16, "vdim": 32, "scale": 0.25, "mask": {"size": 23}, "rot": {"base": 100.0, "dims": 16, "scaling": BANDS}},
 ], ids=lambda m: f"{m['heads']}x{m['kv_heads']}x{m['dim']}x{m['vdim']}")
 def test_window_attention_alone(dtype, m):
     rt = runtime(dtype)
@@ -287,7 +290,8 @@ def plain_latent(x, w, m, kept=None, eps=1e-5):
     {"heads": 4, "dim": 16, "rot_dim": 16, "vdim": 24, "kv_rank": 112, "scale": 0.18, "rot": {"base": 30000.0, "dims": 16}},
     {"heads": 2, "dim": 64, "rot_dim": 32, "vdim": 128, "kv_rank": 128, "scale": 0.1, "rot": {"base": 1000.0, "dims": 32}},
     {"heads": 10, "dim": 16, "rot_dim": 16, "vdim": 16, "kv_rank": 32, "scale": 0.2},
-    {"heads": 3, "dim": 32, "rot_dim": 16, "vdim": 32, "kv_rank": 64, "scale": 0.12, "rot": {"base": 500.0, "dims": 16}},
+    {"heads": 12, "dim": 32, "rot_dim": 16, "vdim": 32, "kv_rank": 64, "scale": 0.12, "rot": {"base": 500.0, "dims": 16}},
+    {"heads": 16, "dim": 16, "rot_dim": 16, "vdim": 16, "kv_rank": 48, "scale": 0.2, "rot": {"base": 50.0, "dims": 8}},
     {"heads": 2, "dim": 32, "rot_dim": 64, "vdim": 64, "kv_rank": 128, "scale": 0.09, "rot": {"base": 10000.0, "dims": 64}},
     {"heads": 1, "dim": 8, "rot_dim": 8, "vdim": 8, "kv_rank": 24, "scale": 0.3, "rot": {"base": 10.0, "dims": 4}},
 ], ids=lambda m: f"{m['heads']}x{m['dim']}+{m['rot_dim']}x{m['vdim']}r{m['kv_rank']}")
