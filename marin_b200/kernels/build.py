@@ -208,6 +208,17 @@ def attention_tc_name(d: int, group: int, dv: int = 0, values_in_keys: bool = Fa
     return f"mb_attention_tc_d{d}_g{group}" if not values_in_keys else f"mb_attention_tc_d{d}_v{dv}_g{group}_vk"
 
 
+#: One or two layouts of every source that is otherwise compiled for a model's own sizes when it first runs (the names and
+#: defines are those the wrappers in ``ops`` use): sink attention with keys and values of their own and over a shared latent
+#: with sixteen heads a CTA, sigmoid attention, chunked linear attention.
+PER_LAYOUT_SAMPLES = {
+    "mb_attention_sink_fast_d128_v128_g4": (["attention_sink_fast.cu"], ["HEAD_DIM=128", "V_DIM=128", "GROUP=4"]),
+    "mb_attention_sink_fast_d160_v128_g16_vk": (["attention_sink_fast.cu"], ["HEAD_DIM=160", "V_DIM=128", "GROUP=16", "V_IN_K"]),
+    "mb_attention_sigmoid_fast_d128_v128_g4": (["attention_sigmoid_fast.cu"], ["HEAD_DIM=128", "V_DIM=128", "GROUP=4"]),
+    "mb_linear_attention_chunked_d128_v32": (["linear_attention_chunked.cu"], ["QK_DIM=128", "V_SLICE=32"]),
+}
+
+
 def build_all(verbose: bool = True) -> List[str]:
     """Compiles every library and the attention kernels for the layouts in ``ATTENTION_LAYOUTS`` (in parallel).
     Used by the build check and before timing."""
@@ -218,6 +229,7 @@ def build_all(verbose: bool = True) -> List[str]:
             jobs[f"mb_attention_tc_d{d}_g{g}"] = attention_tc_job(d, g)
     for d, dv, g in LATENT_LAYOUTS:
         jobs[attention_tc_name(d, g, dv, True)] = attention_tc_job(d, g, dv, True)
+    jobs.update(PER_LAYOUT_SAMPLES)
     return build_many(jobs, verbose)
 
 
