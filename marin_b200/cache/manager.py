@@ -69,6 +69,9 @@ class PagedGroup:
     pool: GroupPool
     k: Optional[torch.Tensor] = None
     v: Optional[torch.Tensor] = None
+    #: pooled rows (``PagedKV.pooled``): ``[entries, pages, kv_heads, rows per page, head_dim]``, the same page ids as k and v
+    k_pool: Optional[torch.Tensor] = None
+    v_pool: Optional[torch.Tensor] = None
 
 
 class RequestCache:
@@ -98,6 +101,8 @@ class PagedView:
     slot_mapping: torch.Tensor    # int32 [tokens]: page * page_size + offset where each new token goes
     page_size: int
     owner: bool                   # False: this run reads another run's cache and writes nothing
+    k_pool: Optional[torch.Tensor] = None    # [pages, kv_heads, pooled rows per page, head_dim] where the need keeps pooled blocks
+    v_pool: Optional[torch.Tensor] = None
 
 
 @dataclass
@@ -122,23 +127,37 @@ class CacheManager:
         self._lib = host_lib()
         self._handle = None
         self.groups: List[PagedGroup] = []
-        self.place: Dict[int, Tuple[int, int]] = {}     # schedule index → (group, index inside group)
-        self.state_needs: Dict[int, StateNeed] = {}
-        self.state: Dict[int, torch.Tensor] = {}
+        #: schedule index → where its need lies: (group, index inside the group) for pages, ("state", key of ``state``) for a
+        #: slot (the key is the schedule index, or for an entry that keeps several things the index followed by the need's
+        #: place among them), or for such an entry a tuple of places in the order of its needs (tuples may nest)
+        self.place: Dict[int, tuple] = {}
+        self.state_needs: Dict[object, StateNeed] = {}
+        self.state: Dict[object, torch.Tensor] = {}
         self.cache_of = list(cache_of)
         by_need: Dict[PagedKV, int] = {}
-        for i, need in enumerate(needs):
+
+        def put(need, key):
             if isinstance(need, PagedKV):
                 if need not in by_need:
                     by_need[need] = len(self.groups)
                     self.groups.append(PagedGroup(need, [], GroupPool(self._lib, self._core, len(self.groups), self.num_pages)))
                 g = by_need[need]
-                self.place[i] = (g, len(self.groups[g].entries))
-                self.groups[g].entries.append(i)
-            elif isinstance(need, StateNeed):
-                self.state_needs[i] = need
-            elif need is not None:
-                raise TypeError(f"schedule entry {i}: unknown cache need {need!r}")
+                self.groups[g].entries.append(key[0])
+                return (g, len(self.groups[g].entries) - 1)
+            if isinstance(need, StateNeed):
+                key = key[0] if len(key) == 1 else key
+                self.state_needs[key] = need
+                return ("state", key)
+            if isinstance(need, (tuple, list)):
+                return tuple(put(n, key + (j,)) for j, n in enumerate(need))
+            if need is None:
+                return None
+            raise TypeError(f"schedule entry {key[0]}: unknown cache need {need!r}")
+
+        for i, need in enumerate(needs):
+            where = put(need, (i,))
+            if where is not None:
+                self.place[i] = where
         windows = (ctypes.c_int * max(1, len(self.groups)))(*[g.need.window if g.need.window else -1 for g in self.groups])
         self._handle = self._lib.mbh_cache_create(self.page_size, self.num_pages, self.max_requests, len(self.groups), windows)
         if not self._handle:
@@ -165,7 +184,7 @@ class CacheManager:
     # ---- device memory -------------------------------------------------------------------------
     def bytes_per_page(self, dtype: torch.dtype) -> int:
         """Bytes one page takes in every group together (``num_pages`` of them are allocated per group)."""
-        return sum(len(g.entries) * self.page_size * g.need.bytes_per_token(dtype) for g in self.groups)
+        return sum(len(g.entries) * self.page_size * g.need.bytes_per_token(dtype, self.page_size) for g in self.groups)
 
     def state_bytes(self) -> int:
         return sum((self.max_requests + 1) * need.bytes() for need in self.state_needs.values())
@@ -176,6 +195,10 @@ class CacheManager:
             g.k = torch.zeros(shape + (g.need.head_dim,), device=device, dtype=dtype)
             # (a latent that keys and values share: the values are the start of the key rows, the view hands out the key pages)
             g.v = g.k if g.need.values_in_keys else torch.zeros(shape + (g.need.value_dim,), device=device, dtype=dtype)
+            if g.need.pooled:
+                shape = shape[:3] + (g.need.pooled_rows(self.page_size),)
+                g.k_pool = torch.zeros(shape + (g.need.head_dim,), device=device, dtype=dtype)
+                g.v_pool = g.k_pool if g.need.values_in_keys else torch.zeros(shape + (g.need.value_dim,), device=device, dtype=dtype)
         # one slot more than there can be requests: the rows that pad a captured batch read and write the spare slot
         for i, need in self.state_needs.items():
             self.state[i] = torch.zeros((self.max_requests + 1, *need.shape), device=device, dtype=need.dtype)

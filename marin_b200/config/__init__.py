@@ -4,5 +4,6 @@ from .fegarax import FegaraxConfig
 from .lakulix import LakulixConfig
 from .nirotar import NirotarConfig
 from .qwen3 import Qwen3Config
+from .vogunex import VogunexConfig
 
-__all__ = ["ConfigError", "FegaraxConfig", "LakulixConfig", "ModelConfig", "NirotarConfig", "Qwen3Config", "load_config", "read_json"]
+__all__ = ["ConfigError", "FegaraxConfig", "LakulixConfig", "ModelConfig", "NirotarConfig", "Qwen3Config", "VogunexConfig", "load_config", "read_json"]

@@ -227,3 +227,153 @@ MB_API int mb_relu2(void* x, int dtype, size_t total, cudaStream_t s) {
     if (dtype == MB_BF16) return launch_kernel(relu2_kernel<bf16>, blocks_for(total, 256), 256, 0, s, 0, (bf16*)x, total);
     return MB_ERR_BAD_DTYPE;
 }
+
+// ---- bias and activation in place: x[t, i] <- act(x[t, i] + b[i]); act 0: none, 1: gelu (erf), 2: gelu (tanh form) ---------
+__device__ __forceinline__ float gelu_erf_f(float v) { return 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f)); }
+__device__ __forceinline__ float gelu_tanh_f(float v) { return 0.5f * v * (1.0f + tanhf(0.79788456080286535588f * (v + 0.044715f * v * v * v))); }
+
+template <typename T>
+__global__ void bias_act_kernel(T* __restrict__ x, const float* __restrict__ b, size_t total, int n, int act) {
+    PDL_ENTER();
+    x = pdl_fresh(x);
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; idx < total; idx += stride) {
+        float v = to_f32(x[idx]) + (b != nullptr ? b[idx % (size_t)n] : 0.0f);
+        if (act == 1) v = gelu_erf_f(v);
+        else if (act == 2) v = gelu_tanh_f(v);
+        x[idx] = from_f32<T>(v);
+    }
+}
+
+MB_API int mb_bias_act(void* x, int dtype, const float* b, int rows, int n, int act, cudaStream_t s) {
+    const size_t total = (size_t)rows * n;
+    if (total == 0) return 0;
+    if (act < 0 || act > 2) return MB_ERR_BAD_SIZE;
+    if (dtype == MB_F32) return launch_kernel(bias_act_kernel<float>, blocks_for(total, 256), 256, 0, s, 0, (float*)x, b, total, n, act);
+    if (dtype == MB_BF16) return launch_kernel(bias_act_kernel<bf16>, blocks_for(total, 256), 256, 0, s, 0, (bf16*)x, b, total, n, act);
+    return MB_ERR_BAD_DTYPE;
+}
+
+// ---- a gated activation with capped inputs: out[t, c] = g sigmoid(alpha g) (u + shift) * row_scale ------------------------
+// rows: [tokens][stride]: ff gate columns, then ff up columns; g = min(gate, limit), u = clamp(up, -limit, limit) where
+// limit > 0 (else as they are).  scale_col >= 0: the row is multiplied by sigmoid(rows[t][scale_col]) (a number per token).
+template <typename T>
+__global__ void glu_capped_kernel(const T* __restrict__ rows, int stride, T* __restrict__ out, int tokens, int ff, float limit, float alpha,
+                                  float shift, int scale_col) {
+    PDL_ENTER();
+    rows = pdl_fresh(rows);
+    const size_t total = (size_t)tokens * ff;
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t step = (size_t)gridDim.x * blockDim.x;
+    for (; idx < total; idx += step) {
+        const size_t t = idx / (size_t)ff;
+        const int c = (int)(idx - t * ff);
+        const T* row = rows + t * stride;
+        float g = to_f32(row[c]), u = to_f32(row[ff + c]);
+        if (limit > 0.0f) { g = fminf(g, limit); u = fminf(fmaxf(u, -limit), limit); }
+        float v = g / (1.0f + expf(-alpha * g)) * (u + shift);
+        if (scale_col >= 0) v *= 1.0f / (1.0f + expf(-to_f32(row[scale_col])));
+        out[idx] = from_f32<T>(v);
+    }
+}
+
+MB_API int mb_glu_capped(const void* rows, int stride, int dtype, void* out, int tokens, int ff, float limit, float alpha, float shift,
+                         int scale_col, cudaStream_t s) {
+    const size_t total = (size_t)tokens * ff;
+    if (total == 0) return 0;
+    if (stride < 2 * ff || scale_col >= stride) return MB_ERR_BAD_SIZE;
+    if (dtype == MB_F32)
+        return launch_kernel(glu_capped_kernel<float>, blocks_for(total, 256), 256, 0, s, 0, (const float*)rows, stride, (float*)out, tokens, ff,
+                             limit, alpha, shift, scale_col);
+    if (dtype == MB_BF16)
+        return launch_kernel(glu_capped_kernel<bf16>, blocks_for(total, 256), 256, 0, s, 0, (const bf16*)rows, stride, (bf16*)out, tokens, ff,
+                             limit, alpha, shift, scale_col);
+    return MB_ERR_BAD_DTYPE;
+}
+
+// ---- a gate per head, in place: x[t, a, :] *= sigmoid(g[t, a]);  g: [tokens][g_stride] at column g_col -------------------
+template <typename T>
+__global__ void head_gate_kernel(T* __restrict__ x, const T* __restrict__ g, int g_stride, int g_col, size_t total, int heads, int dim) {
+    PDL_ENTER();
+    x = pdl_fresh(x); g = pdl_fresh(g);
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t step = (size_t)gridDim.x * blockDim.x;
+    const size_t row = (size_t)heads * dim;
+    for (; idx < total; idx += step) {
+        const size_t t = idx / row;
+        const int a = (int)((idx - t * row) / dim);
+        const float gate = 1.0f / (1.0f + expf(-to_f32(g[t * g_stride + g_col + a])));
+        x[idx] = from_f32<T>(to_f32(x[idx]) * gate);
+    }
+}
+
+MB_API int mb_head_gate(void* x, int dtype, const void* g, int g_stride, int g_col, int tokens, int heads, int dim, cudaStream_t s) {
+    const size_t total = (size_t)tokens * heads * dim;
+    if (total == 0) return 0;
+    if (dtype == MB_F32)
+        return launch_kernel(head_gate_kernel<float>, blocks_for(total, 256), 256, 0, s, 0, (float*)x, (const float*)g, g_stride, g_col, total, heads, dim);
+    if (dtype == MB_BF16)
+        return launch_kernel(head_gate_kernel<bf16>, blocks_for(total, 256), 256, 0, s, 0, (bf16*)x, (const bf16*)g, g_stride, g_col, total, heads, dim);
+    return MB_ERR_BAD_DTYPE;
+}
+
+// ---- the last row of every request of the step, kept for the next step's token shift: carry[slot] = h[last token] --------
+template <typename T>
+__global__ void keep_last_row_kernel(const T* __restrict__ h, float* __restrict__ carry, long long state_stride, const int* __restrict__ cu_tokens,
+                                     const int* __restrict__ state_slots, int n) {
+    PDL_ENTER();
+    h = pdl_fresh(h);
+    const int req = blockIdx.x;
+    const int first = cu_tokens[req], end = cu_tokens[req + 1];
+    if (end <= first) return;
+    float* dst = carry + (size_t)state_slots[req] * state_stride;
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < n; i += gridDim.y * blockDim.x) dst[i] = to_f32(h[(size_t)(end - 1) * n + i]);
+}
+
+MB_API int mb_keep_last_row(const void* h, int dtype, float* carry, long long state_stride, const int* cu_tokens, const int* state_slots,
+                            int requests, int n, cudaStream_t s) {
+    if (requests <= 0 || n <= 0) return 0;
+    dim3 grid(requests, (n + 255) / 256);
+    if (dtype == MB_F32) return launch_kernel(keep_last_row_kernel<float>, grid, 256, 0, s, 0, (const float*)h, carry, state_stride, cu_tokens, state_slots, n);
+    if (dtype == MB_BF16) return launch_kernel(keep_last_row_kernel<bf16>, grid, 256, 0, s, 0, (const bf16*)h, carry, state_stride, cu_tokens, state_slots, n);
+    return MB_ERR_BAD_DTYPE;
+}
+
+// ---- a bias added to every row of the float32 residual: y[t, i] += b[i] -----------------------------------------------------
+__global__ void add_row_bias_kernel(float* __restrict__ y, const float* __restrict__ b, size_t total, int n) {
+    PDL_ENTER();
+    y = pdl_fresh(y);
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t step = (size_t)gridDim.x * blockDim.x;
+    for (; idx < total; idx += step) y[idx] += b[idx % (size_t)n];
+}
+
+MB_API int mb_add_row_bias(float* y, const float* b, int rows, int n, cudaStream_t s) {
+    const size_t total = (size_t)rows * n;
+    if (total == 0) return 0;
+    return launch_kernel(add_row_bias_kernel, blocks_for(total, 256), 256, 0, s, 0, y, b, total, n);
+}
+
+// ---- RMS norm of a column block of wider rows: out[t, :] = x[t, col : col + n] / rms * w, a block per row ------------------
+template <typename T>
+__global__ void __launch_bounds__(256) rmsnorm_cols_kernel(const T* __restrict__ x, int stride, int col, const float* __restrict__ w, float eps,
+                                                           T* __restrict__ out, int n) {
+    PDL_ENTER();
+    x = pdl_fresh(x);
+    __shared__ float scratch[32];
+    const T* row = x + (size_t)blockIdx.x * stride + col;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) { const float v = to_f32(row[i]); ss = fmaf(v, v, ss); }
+    ss = block_sum(ss, scratch);
+    const float factor = 1.0f / sqrtf(ss / (float)n + eps);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) out[(size_t)blockIdx.x * n + i] = from_f32<T>(to_f32(row[i]) * factor * w[i]);
+}
+
+MB_API int mb_rmsnorm_cols(const void* x, int stride, int col, int dtype, const float* w, float eps, void* out, int rows, int n, cudaStream_t s) {
+    if (rows <= 0 || n <= 0) return 0;
+    if (col < 0 || col + n > stride) return MB_ERR_BAD_SIZE;
+    if (dtype == MB_F32) return launch_kernel(rmsnorm_cols_kernel<float>, rows, 256, 0, s, 0, (const float*)x, stride, col, w, eps, (float*)out, n);
+    if (dtype == MB_BF16) return launch_kernel(rmsnorm_cols_kernel<bf16>, rows, 256, 0, s, 0, (const bf16*)x, stride, col, w, eps, (bf16*)out, n);
+    return MB_ERR_BAD_DTYPE;
+}

@@ -24,9 +24,10 @@ template <typename T>
 __global__ void __launch_bounds__(LF_THREADS) latent_finish_kernel(
     const T* __restrict__ row, int row_stride, T* __restrict__ q_out, const float* __restrict__ c_weight, float eps,
     const int* __restrict__ positions, const float* __restrict__ inv_freq, int rot_dims, int interleaved,
-    const int* __restrict__ slot_mapping, T* __restrict__ k_cache, int H, int dn, int dr, int r, int page_size, int write_kv) {
+    const int* __restrict__ slot_mapping, T* __restrict__ k_cache, int H, int dn, int dr, int r, int page_size, int write_kv,
+    const T* __restrict__ kv_row, int kv_stride) {
     PDL_ENTER();
-    row = pdl_fresh(row);
+    row = pdl_fresh(row); kv_row = pdl_fresh(kv_row);
     extern __shared__ float smem[];
     float* cs_tab = smem;                      // [half] cosines, [half] sines
     const int half = rot_dims >> 1;
@@ -61,7 +62,9 @@ __global__ void __launch_bounds__(LF_THREADS) latent_finish_kernel(
     }
     if (!write_kv) return;
     const int slot = slot_mapping[t];
-    const T* kv = src + (size_t)H * (dn + dr);
+    // the latent and the key part: behind the queries in the same row, or (queries that went through a latent of their own
+    // come from a second product) in rows of their own
+    const T* kv = kv_row != nullptr ? kv_row + (size_t)t * kv_stride : src + (size_t)H * (dn + dr);
     float ss = 0.0f;
     for (int i = threadIdx.x; i < D; i += LF_THREADS) {
         const float v = to_f32(kv[i]);
@@ -93,7 +96,7 @@ __global__ void __launch_bounds__(LF_THREADS) latent_finish_kernel(
 
 MB_API int mb_latent_finish(const void* row, int row_stride, int dtype, void* q_out, const float* c_weight, float eps, const int* positions,
                             const float* inv_freq, int rot_dims, int interleaved, const int* slot_mapping, void* k_cache, int tokens, int H,
-                            int dn, int dr, int r, int page_size, int write_kv, cudaStream_t s) {
+                            int dn, int dr, int r, int page_size, int write_kv, const void* kv_row, int kv_stride, cudaStream_t s) {
     if (tokens <= 0) return 0;
     if (H <= 0 || dn < 0 || dr < 0 || r <= 0 || rot_dims < 0 || rot_dims > dr || (rot_dims & 1)) return MB_ERR_BAD_SIZE;
     if (inv_freq == nullptr) rot_dims = 0;
@@ -101,10 +104,12 @@ MB_API int mb_latent_finish(const void* row, int row_stride, int dtype, void* q_
     if (smem > 48 * 1024) return MB_ERR_BAD_SIZE;
     if (dtype == MB_F32)
         return launch_kernel(latent_finish_kernel<float>, tokens, LF_THREADS, smem, s, 0, (const float*)row, row_stride, (float*)q_out, c_weight,
-                             eps, positions, inv_freq, rot_dims, interleaved, slot_mapping, (float*)k_cache, H, dn, dr, r, page_size, write_kv);
+                             eps, positions, inv_freq, rot_dims, interleaved, slot_mapping, (float*)k_cache, H, dn, dr, r, page_size, write_kv,
+                             (const float*)kv_row, kv_stride);
     if (dtype == MB_BF16)
         return launch_kernel(latent_finish_kernel<bf16>, tokens, LF_THREADS, smem, s, 0, (const bf16*)row, row_stride, (bf16*)q_out, c_weight,
-                             eps, positions, inv_freq, rot_dims, interleaved, slot_mapping, (bf16*)k_cache, H, dn, dr, r, page_size, write_kv);
+                             eps, positions, inv_freq, rot_dims, interleaved, slot_mapping, (bf16*)k_cache, H, dn, dr, r, page_size, write_kv,
+                             (const bf16*)kv_row, kv_stride);
     return MB_ERR_BAD_DTYPE;
 }
 

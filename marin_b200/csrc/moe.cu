@@ -2,6 +2,8 @@
 // and the token goes through those experts only.  Expert: down( silu(gate x) * (up x) ), no biases; or, `act_mode` 1, an
 // expert without a gate, down( relu(up x)^2 ), whose first matrix is [experts][ff][h].  Instead of a router a table may
 // name every token id's experts (mb_moe_table_route): the choice then depends on the token alone, with equal weights.
+// The gated form is g sigmoid(alpha g) (u + shift) with g = gate x and u = up x, both capped where `act_limit` > 0
+// (g <- min(g, limit), u <- clamp(u, -limit, limit)); alpha 1, shift 0 and no limit is silu(gate x) * (up x).
 //   * router: z = W_r h in float32, score = sigmoid(z) or the softmax of z over the experts; the chosen experts' scores are
 //     the weights, renormalised to sum 1 over the chosen ones if asked;
 //   * the weight multiplies the expert's input (x = w h, the activation sees it) or its output (x = h, result times w).
@@ -29,7 +31,7 @@ __host__ __device__ __forceinline__ int gate_up_row(int c, int which, int ff, in
 // row in a fixed order, so a token's logits do not depend on the batch.
 template <typename T>
 __global__ void __launch_bounds__(MR_THREADS) moe_route_kernel(const T* __restrict__ h_rows, const float* __restrict__ router,
-                                                               int* __restrict__ expert_out, float* __restrict__ weight_out,
+                                                               const float* __restrict__ router_bias, int* __restrict__ expert_out, float* __restrict__ weight_out,
                                                                int tokens, int h, int E, int top, int score_mode, int renorm) {
     PDL_ENTER();
     h_rows = pdl_fresh(h_rows);
@@ -70,7 +72,7 @@ __global__ void __launch_bounds__(MR_THREADS) moe_route_kernel(const T* __restri
         }
         for (; i < h; i += 32) d0 = fmaf(xrow[i], w[i], d0);
         const float dot = warp_sum((d0 + d1) + (d2 + d3));
-        if (lane == 0) z[e] = dot;
+        if (lane == 0) z[e] = router_bias != nullptr ? dot + router_bias[e] : dot;
     }
     __syncthreads();
     if (warp != 0) return;
@@ -111,17 +113,17 @@ __global__ void __launch_bounds__(MR_THREADS) moe_route_kernel(const T* __restri
         for (int c = 0; c < top; ++c) weight_out[(size_t)t * top + c] /= chosen_sum;
 }
 
-MB_API int mb_moe_route(const void* h_rows, int dtype, const float* router, int* expert_out, float* weight_out, int tokens, int h,
+MB_API int mb_moe_route(const void* h_rows, int dtype, const float* router, const float* router_bias, int* expert_out, float* weight_out, int tokens, int h,
                         int E, int top, int score_mode, int renorm, cudaStream_t s) {
     if (tokens <= 0) return 0;
     if (E <= 0 || top <= 0 || top > E || h <= 0 || score_mode < 0 || score_mode > 1) return MB_ERR_BAD_SIZE;
     const size_t smem = (size_t)(E + h) * sizeof(float);
     if (smem > 48 * 1024) return MB_ERR_BAD_SIZE;
     if (dtype == MB_F32)
-        return launch_kernel(moe_route_kernel<float>, tokens, MR_THREADS, smem, s, 0, (const float*)h_rows, router, expert_out,
+        return launch_kernel(moe_route_kernel<float>, tokens, MR_THREADS, smem, s, 0, (const float*)h_rows, router, router_bias, expert_out,
                              weight_out, tokens, h, E, top, score_mode, renorm);
     if (dtype == MB_BF16)
-        return launch_kernel(moe_route_kernel<bf16>, tokens, MR_THREADS, smem, s, 0, (const bf16*)h_rows, router, expert_out,
+        return launch_kernel(moe_route_kernel<bf16>, tokens, MR_THREADS, smem, s, 0, (const bf16*)h_rows, router, router_bias, expert_out,
                              weight_out, tokens, h, E, top, score_mode, renorm);
     return MB_ERR_BAD_DTYPE;
 }
@@ -185,7 +187,8 @@ template <typename T>
 __global__ void __launch_bounds__(ME_THREADS) moe_gate_up_kernel(const T* __restrict__ h_rows, const T* __restrict__ w_gate_up,
                                                                  const int* __restrict__ expert_of, const float* __restrict__ weight_of,
                                                                  T* __restrict__ act, int h, int ff, int top, int weight_on_input,
-                                                                 int interleaved, int act_mode) {
+                                                                 int interleaved, int act_mode, float act_limit, float act_alpha,
+                                                                 float act_shift) {
     PDL_ENTER();
     h_rows = pdl_fresh(h_rows); expert_of = pdl_fresh(expert_of); weight_of = pdl_fresh(weight_of);
     extern __shared__ float x[];               // [h]
@@ -215,7 +218,8 @@ __global__ void __launch_bounds__(ME_THREADS) moe_gate_up_kernel(const T* __rest
         for (int i = lane; i < h; i += 32) { dg = fmaf(x[i], to_f32(g[i]), dg); du = fmaf(x[i], to_f32(u[i]), du); }
         dg = warp_sum(dg);
         du = warp_sum(du);
-        if (lane == 0) act[(size_t)p * ff + c] = from_f32<T>(dg / (1.0f + expf(-dg)) * du);
+        if (act_limit > 0.0f) { dg = fminf(dg, act_limit); du = fminf(fmaxf(du, -act_limit), act_limit); }
+        if (lane == 0) act[(size_t)p * ff + c] = from_f32<T>(dg / (1.0f + expf(-act_alpha * dg)) * (du + act_shift));
     }
 }
 
@@ -251,20 +255,20 @@ __global__ void __launch_bounds__(ME_THREADS) moe_down_kernel(const T* __restric
 // which = 0: act <- the activations of every pair; which = 1: y += the chosen experts' outputs, from act.
 MB_API int mb_moe_experts_plain(const void* h_rows, int dtype, const void* w_gate_up, const void* w_down, const int* expert_of,
                                 const float* weight_of, void* act, float* y, int tokens, int h, int ff, int top, int weight_on_input,
-                                int interleaved, int which, int act_mode, cudaStream_t s) {
+                                int interleaved, int which, int act_mode, float act_limit, float act_alpha, float act_shift, cudaStream_t s) {
     if (tokens <= 0) return 0;
     if (h <= 0 || ff <= 0 || top <= 0 || (size_t)h * 4 > 48 * 1024 || (size_t)ff * 4 > 48 * 1024) return MB_ERR_BAD_SIZE;
     if (dtype == MB_F32) {
         if (which == 0)
             return launch_kernel(moe_gate_up_kernel<float>, tokens * top, ME_THREADS, (size_t)h * 4, s, 0, (const float*)h_rows,
-                                 (const float*)w_gate_up, expert_of, weight_of, (float*)act, h, ff, top, weight_on_input, interleaved, act_mode);
+                                 (const float*)w_gate_up, expert_of, weight_of, (float*)act, h, ff, top, weight_on_input, interleaved, act_mode, act_limit, act_alpha, act_shift);
         return launch_kernel(moe_down_kernel<float>, tokens, ME_THREADS, (size_t)ff * 4, s, 0, (const float*)act, (const float*)w_down,
                              expert_of, weight_of, y, h, ff, top, weight_on_input);
     }
     if (dtype == MB_BF16) {
         if (which == 0)
             return launch_kernel(moe_gate_up_kernel<bf16>, tokens * top, ME_THREADS, (size_t)h * 4, s, 0, (const bf16*)h_rows,
-                                 (const bf16*)w_gate_up, expert_of, weight_of, (bf16*)act, h, ff, top, weight_on_input, interleaved, act_mode);
+                                 (const bf16*)w_gate_up, expert_of, weight_of, (bf16*)act, h, ff, top, weight_on_input, interleaved, act_mode, act_limit, act_alpha, act_shift);
         return launch_kernel(moe_down_kernel<bf16>, tokens, ME_THREADS, (size_t)ff * 4, s, 0, (const bf16*)act, (const bf16*)w_down,
                              expert_of, weight_of, y, h, ff, top, weight_on_input);
     }
@@ -314,7 +318,8 @@ template <int MODE, int GMT>
 __global__ void __launch_bounds__(128) moe_grouped_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W,
                                                           const int* __restrict__ offsets, int E, int N, int K, bf16* __restrict__ act_out,
                                                           float* __restrict__ f_out, const int* __restrict__ dst_rows,
-                                                          const float* __restrict__ row_scale, int accumulate, int interleaved) {
+                                                          const float* __restrict__ row_scale, int accumulate, int interleaved,
+                                                          float act_limit, float act_alpha, float act_shift) {
     PDL_ENTER();
     A = pdl_fresh(A); offsets = pdl_fresh(offsets); dst_rows = pdl_fresh(dst_rows); row_scale = pdl_fresh(row_scale); f_out = pdl_fresh(f_out);
     constexpr int NB = G_NB_OF(MODE);
@@ -411,9 +416,14 @@ __global__ void __launch_bounds__(128) moe_grouped_kernel(const bf16* __restrict
             for (int j = 0; j < NT; ++j) {
                 const int c = col + j * 8;
                 if (c < N) {                                   // N is even: a pair of columns is inside or outside together
-                    const float g0 = acc[0][j][2 * rr], g1 = acc[0][j][2 * rr + 1];
-                    const float u0 = acc[NB - 1][j][2 * rr], u1 = acc[NB - 1][j][2 * rr + 1];
-                    *reinterpret_cast<uint32_t*>(dst + c) = pack_bf16(g0 / (1.0f + __expf(-g0)) * u0, g1 / (1.0f + __expf(-g1)) * u1);
+                    float g0 = acc[0][j][2 * rr], g1 = acc[0][j][2 * rr + 1];
+                    float u0 = acc[NB - 1][j][2 * rr], u1 = acc[NB - 1][j][2 * rr + 1];
+                    if (act_limit > 0.0f) {                    // capped inputs: g <- min(g, limit), u <- clamp(u, -limit, limit)
+                        g0 = fminf(g0, act_limit); g1 = fminf(g1, act_limit);
+                        u0 = fminf(fmaxf(u0, -act_limit), act_limit); u1 = fminf(fmaxf(u1, -act_limit), act_limit);
+                    }
+                    *reinterpret_cast<uint32_t*>(dst + c) = pack_bf16(g0 / (1.0f + __expf(-act_alpha * g0)) * (u0 + act_shift),
+                                                                      g1 / (1.0f + __expf(-act_alpha * g1)) * (u1 + act_shift));
                 }
             }
         } else if (MODE == 2) {
@@ -471,20 +481,22 @@ static int grouped_rows(int pairs, int E) { return pairs <= 8 * E ? 16 : pairs <
 
 template <int MODE, int GMT>
 static int grouped_launch(const bf16* A, const bf16* W, const int* offsets, int E, int N, int K, bf16* act, float* out, const int* dst_rows,
-                          const float* row_scale, int accumulate, int interleaved, int pairs, cudaStream_t s) {
+                          const float* row_scale, int accumulate, int interleaved, int pairs, cudaStream_t s, float act_limit = 0.0f,
+                          float act_alpha = 1.0f, float act_shift = 0.0f) {
     cudaFuncSetAttribute(moe_grouped_kernel<MODE, GMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, G_SMEM(MODE, GMT));
     return launch_kernel(moe_grouped_kernel<MODE, GMT>, dim3(grouped_tiles(pairs, E, GMT), (N + GN - 1) / GN), 128, G_SMEM(MODE, GMT), s, 0, A, W,
-                         offsets, E, N, K, act, out, dst_rows, row_scale, accumulate, interleaved);
+                         offsets, E, N, K, act, out, dst_rows, row_scale, accumulate, interleaved, act_limit, act_alpha, act_shift);
 }
 
 template <int MODE>
 static int grouped_by_rows(const bf16* A, const bf16* W, const int* offsets, int E, int N, int K, bf16* act, float* out, const int* dst_rows,
-                           const float* row_scale, int accumulate, int interleaved, int pairs, cudaStream_t s) {
+                           const float* row_scale, int accumulate, int interleaved, int pairs, cudaStream_t s, float act_limit = 0.0f,
+                           float act_alpha = 1.0f, float act_shift = 0.0f) {
     switch (grouped_rows(pairs, E)) {
-        case 16: return grouped_launch<MODE, 16>(A, W, offsets, E, N, K, act, out, dst_rows, row_scale, accumulate, interleaved, pairs, s);
-        case 32: return grouped_launch<MODE, 32>(A, W, offsets, E, N, K, act, out, dst_rows, row_scale, accumulate, interleaved, pairs, s);
+        case 16: return grouped_launch<MODE, 16>(A, W, offsets, E, N, K, act, out, dst_rows, row_scale, accumulate, interleaved, pairs, s, act_limit, act_alpha, act_shift);
+        case 32: return grouped_launch<MODE, 32>(A, W, offsets, E, N, K, act, out, dst_rows, row_scale, accumulate, interleaved, pairs, s, act_limit, act_alpha, act_shift);
     }
-    return grouped_launch<MODE, 64>(A, W, offsets, E, N, K, act, out, dst_rows, row_scale, accumulate, interleaved, pairs, s);
+    return grouped_launch<MODE, 64>(A, W, offsets, E, N, K, act, out, dst_rows, row_scale, accumulate, interleaved, pairs, s, act_limit, act_alpha, act_shift);
 }
 
 // The pairs' inputs in expert order: xs bf16 [pairs][h], with each pair's token and weight beside it and where every pair went.
@@ -497,13 +509,13 @@ MB_API int mb_moe_gather(const void* h_rows, const int* order, const float* weig
 
 // act bf16 [pairs][ff] = silu(gate xs) * (up xs), expert by expert; act_mode 1: relu(up xs)^2 with w_gate_up = [E][ff][h].
 MB_API int mb_moe_grouped_gate_up(const void* xs, const void* w_gate_up, const int* offsets, void* act, int pairs, int h, int ff, int E,
-                                  int interleaved, int act_mode, cudaStream_t s) {
+                                  int interleaved, int act_mode, float act_limit, float act_alpha, float act_shift, cudaStream_t s) {
     if (pairs <= 0) return 0;
     if (!mb_moe_fast_supported(h, ff) || E <= 0) return MB_ERR_BAD_SIZE;
     if (act_mode == 1)
         return grouped_by_rows<2>((const bf16*)xs, (const bf16*)w_gate_up, offsets, E, ff, h, (bf16*)act, nullptr, nullptr, nullptr, 0, 0, pairs, s);
     return grouped_by_rows<0>((const bf16*)xs, (const bf16*)w_gate_up, offsets, E, ff, h, (bf16*)act, nullptr, nullptr, nullptr, 0, interleaved,
-                              pairs, s);
+                              pairs, s, act_limit, act_alpha, act_shift);
 }
 
 // out float32 = down act, expert by expert: row i goes to row dst_rows[i] of out (null: row i), times row_scale[i] (null: 1),

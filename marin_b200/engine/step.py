@@ -47,14 +47,22 @@ class CacheViews:
     def view(self, index: int, ctx: StepContext):
         cache = self.cache
         owner_index = cache.cache_of[index] if cache.cache_of[index] is not None else index
-        if owner_index in cache.place:
-            g, j = cache.place[owner_index]
-            group = cache.groups[g]
-            return PagedView(group.k[j], group.v[j], ctx.group_block_tables[g], ctx.group_slot_mappings[g],
-                             cache.page_size, owner=owner_index == index)
-        if owner_index in cache.state:
-            return StateView(cache.state[owner_index], ctx.state_slots, owner=owner_index == index)
-        return None
+        owner = owner_index == index
+
+        def make(where):
+            if where is None:
+                return None
+            if isinstance(where[0], int):
+                g, j = where
+                group = cache.groups[g]
+                return PagedView(group.k[j], group.v[j], ctx.group_block_tables[g], ctx.group_slot_mappings[g], cache.page_size, owner=owner,
+                                 k_pool=group.k_pool[j] if group.k_pool is not None else None,
+                                 v_pool=group.v_pool[j] if group.v_pool is not None else None)
+            if where[0] == "state":
+                return StateView(cache.state[where[1]], ctx.state_slots, owner=owner)
+            return tuple(make(w) for w in where)          # an entry that keeps several things: its views in the order of its needs
+
+        return make(cache.place.get(owner_index))
 
 
 class Runner:

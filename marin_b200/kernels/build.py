@@ -159,6 +159,8 @@ LIBRARIES: Dict[str, List[str]] = {
     "mb_attention_sink": ["attention_sink.cu"],
     "mb_attention_latent": ["attention_latent.cu"],
     "mb_moe": ["moe.cu"],
+    "mb_attention_pooled": ["attention_pooled.cu"],
+    "mb_ssm": ["ssm.cu"],
     "mb_host": ["host/cache_core.cpp", "host/scheduler.cpp", "host/sampler.cpp", "host/safetensors.cpp"],
 }
 

@@ -1423,7 +1423,8 @@ def _sink_split(per_chunk: int, longest: int, places: int) -> int:
 
 # ---- attention over a latent that keys and values share (csrc/attention_latent.cu) -------------------------------------------
 def latent_finish(rows: torch.Tensor, q_out: torch.Tensor, c_weight, eps: float, positions, inv_freq, rot_dims: int, interleaved: bool,
-                  slot_mapping, k_cache, H: int, dn: int, dr: int, r: int, write_kv: bool = True) -> None:
+                  slot_mapping, k_cache, H: int, dn: int, dr: int, r: int, write_kv: bool = True,
+                  kv_rows: Optional[torch.Tensor] = None) -> None:
     """Finishes a fused projection whose rows hold ``H`` query heads of ``dn`` unrotated and ``dr`` rotated numbers and, for a
     layer that owns its cache, ``r`` latent numbers and ``dr`` key numbers.  The queries' rotated parts go, rotated, to
     ``q_out[:, head, r:]`` (``[T, H, r + dr]``; the first ``r`` of every head are left for ``heads_product``); the latent is
@@ -1431,13 +1432,18 @@ def latent_finish(rows: torch.Tensor, q_out: torch.Tensor, c_weight, eps: float,
     _need_cuda(rows, q_out, c_weight, positions, inv_freq, slot_mapping, k_cache)
     T = rows.shape[0]
     D = r + dr
-    assert tuple(q_out.shape) == (T, H * D) and q_out.dtype == rows.dtype and rows.shape[1] >= H * (dn + dr) + (D if write_kv else 0)
+    assert tuple(q_out.shape) == (T, H * D) and q_out.dtype == rows.dtype
+    assert rows.shape[1] >= H * (dn + dr) + (D if write_kv and kv_rows is None else 0)
+    # ``kv_rows``: the latent and the key part come from rows of their own (a column slice ``[T, r + dr]`` of a wider matrix)
+    assert kv_rows is None or (kv_rows.is_cuda and kv_rows.dtype == rows.dtype and tuple(kv_rows.shape) == (T, D) and kv_rows.stride(1) == 1)
     assert not write_kv or (k_cache.dtype == rows.dtype and k_cache.shape[1] == 1 and k_cache.shape[3] == D and c_weight is not None)
     _cost((rows.shape[1] - H * dn) * T * rows.element_size() + T * (H * dr + D) * rows.element_size(), 6.0 * T * (H * dr + D))
     _check(_lib("mb_attention_latent").mb_latent_finish(
         _ptr(rows), _c_int(rows.shape[1]), _code(rows), _ptr(q_out), _ptr(c_weight), _c_float(eps), _ptr(positions), _ptr(inv_freq),
         _c_int(rot_dims if inv_freq is not None else 0), _c_int(int(interleaved)), _ptr(slot_mapping), _ptr(k_cache), _c_int(T), _c_int(H),
-        _c_int(dn), _c_int(dr), _c_int(r), _c_int(k_cache.shape[2] if write_kv else 0), _c_int(int(write_kv)), _stream()), "latent heads")
+        _c_int(dn), _c_int(dr), _c_int(r), _c_int(k_cache.shape[2] if write_kv else 0), _c_int(int(write_kv)),
+        _c_void_p(kv_rows.data_ptr()) if kv_rows is not None else None, _c_int(kv_rows.stride(0) if kv_rows is not None else 0), _stream()),
+        "latent heads")
 
 
 #: bf16 products per head go to the tensor-core kernel where the layout allows (False: always the plain kernel)
@@ -1464,16 +1470,17 @@ SCORE_MODES = {"sigmoid": 0, "softmax": 1}
 
 
 def moe_route(x: torch.Tensor, router: torch.Tensor, experts_out: torch.Tensor, weights_out: torch.Tensor, score: str = "sigmoid",
-              renormalize: bool = False) -> None:
-    """Router logits ``x router^T`` in float32, scores by ``score``, the ``top`` best experts per token (``top`` = the outputs'
+              renormalize: bool = False, bias: Optional[torch.Tensor] = None) -> None:
+    """Router logits ``x router^T (+ bias)`` in float32, scores by ``score``, the ``top`` best experts per token (``top`` = the outputs'
     second size) in order of decreasing score, the lower expert among equals; their scores are the weights."""
     _need_cuda(x, router, experts_out, weights_out)
     T, h = x.shape
     E, top = router.shape[0], experts_out.shape[1]
     assert router.dtype == torch.float32 and router.shape[1] == h and experts_out.dtype == torch.int32 and weights_out.dtype == torch.float32
     assert tuple(experts_out.shape) == (T, top) and tuple(weights_out.shape) == (T, top)
+    assert bias is None or (bias.is_cuda and bias.dtype == torch.float32 and bias.numel() == E)
     _cost(_size(x) + _size(router) + _size(experts_out) * 2, 2.0 * T * E * h)
-    _check(_lib("mb_moe").mb_moe_route(_ptr(x), _code(x), _ptr(router), _ptr(experts_out), _ptr(weights_out), _c_int(T), _c_int(h), _c_int(E),
+    _check(_lib("mb_moe").mb_moe_route(_ptr(x), _code(x), _ptr(router), _ptr(bias), _ptr(experts_out), _ptr(weights_out), _c_int(T), _c_int(h), _c_int(E),
                                       _c_int(top), _c_int(SCORE_MODES[score]), _c_int(int(renormalize)), _stream()), "router")
 
 
@@ -1498,11 +1505,23 @@ def moe_group(experts: torch.Tensor, E: int, offsets: torch.Tensor, order: torch
     _check(_lib("mb_moe").mb_moe_group(_ptr(experts), _c_int(pairs), _c_int(E), _ptr(offsets), _ptr(order), _stream()), "pairs grouped")
 
 
-EXPERT_ACTIVATIONS = {"swiglu": 0, "relu2": 1}
+EXPERT_ACTIVATIONS = {"swiglu": 0, "relu2": 1, "glu_capped": 0}
+#: the gated form ``g sigmoid(alpha g) (u + shift)`` with both inputs capped at ``limit`` (0: not capped), as (limit, alpha, shift);
+#: "swiglu" is this
+SILU_FORM = (0.0, 1.0, 0.0)
+
+
+def _glu_form(activation: str, form) -> tuple:
+    if activation == "glu_capped":
+        if form is None:
+            raise KernelError("glu_capped: the form (limit, alpha, shift) is needed")
+        return tuple(float(v) for v in form)
+    return SILU_FORM
 
 
 def moe_experts_plain(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, experts: torch.Tensor, weights: torch.Tensor,
-                      act: torch.Tensor, y: torch.Tensor, weight_on_input: bool, interleaved: bool = False, activation: str = "swiglu") -> None:
+                      act: torch.Tensor, y: torch.Tensor, weight_on_input: bool, interleaved: bool = False, activation: str = "swiglu",
+                      form=None) -> None:
     """``y[t] += sum_c down_e( silu(gate_e x) * (up_e x) )`` over token ``t``'s chosen experts ``e`` in choice order, ``x = w h[t]``
     where the weight goes on the input, else the result times ``w``.  Any sizes, both dtypes.  ``interleaved``: an expert's
     gate and up rows alternate in blocks of 16 (``interleave_gate_up``) instead of gate rows first.  ``activation`` "relu2":
@@ -1511,7 +1530,8 @@ def moe_experts_plain(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Te
     T, h = x.shape
     top = experts.shape[1]
     ff = w_down.shape[2]
-    gated = activation == "swiglu"
+    gated = activation != "relu2"
+    limit, alpha, shift = _glu_form(activation, form)
     assert tuple(w_gate_up.shape[1:]) == ((2 if gated else 1) * ff, h) and tuple(w_down.shape[1:]) == (h, ff) and w_gate_up.dtype == x.dtype == w_down.dtype
     assert act.dtype == x.dtype and act.numel() >= T * top * ff and y.dtype == torch.float32 and tuple(y.shape) == (T, h)
     pairs = T * top
@@ -1523,7 +1543,8 @@ def moe_experts_plain(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Te
             _cost(touched * ff * h * x.element_size() + pairs * ff * x.element_size() + 2 * _size(y), 2.0 * pairs * ff * h)
         _check(_lib("mb_moe").mb_moe_experts_plain(_ptr(x), _code(x), _ptr(w_gate_up), _ptr(w_down), _ptr(experts), _ptr(weights), _ptr(act),
                                                   _ptr(y), _c_int(T), _c_int(h), _c_int(ff), _c_int(top), _c_int(int(weight_on_input)),
-                                                  _c_int(int(interleaved)), _c_int(which), _c_int(EXPERT_ACTIVATIONS[activation]), _stream()), what)
+                                                  _c_int(int(interleaved)), _c_int(which), _c_int(EXPERT_ACTIVATIONS[activation]), _c_float(limit),
+                                                  _c_float(alpha), _c_float(shift), _stream()), what)
 
 
 #: bf16 experts go to the grouped tensor-core kernels where the sizes allow (False: always the plain kernels)
@@ -1557,7 +1578,7 @@ def _expert_streams(device, n: int):
 
 
 def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, experts: torch.Tensor, weights: torch.Tensor,
-                y: torch.Tensor, weight_on_input: bool, workspace, interleaved: bool = False, activation: str = "swiglu") -> None:
+                y: torch.Tensor, weight_on_input: bool, workspace, interleaved: bool = False, activation: str = "swiglu", form=None) -> None:
     """The chosen experts' outputs added into ``y`` (float32 ``[T, h]``); see ``moe_experts_plain``.  bf16 with sizes in steps
     of 64: the pairs are sorted by expert on the device and their inputs gathered in that order; then either two grouped
     products over all experts (few pairs: single-token steps, captured or not: nothing is read back), or, with many pairs
@@ -1567,10 +1588,11 @@ def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, 
     pairs = T * top
     act = workspace.get("moe_act", (pairs, ff), x.dtype)
     if not (use_fast_experts and x.dtype == torch.bfloat16 and fast_experts_supported(h, ff)):
-        moe_experts_plain(x, w_gate_up, w_down, experts, weights, act, y, weight_on_input, interleaved, activation)
+        moe_experts_plain(x, w_gate_up, w_down, experts, weights, act, y, weight_on_input, interleaved, activation, form)
         return
     _need_cuda(x, w_gate_up, w_down, experts, weights, y)
-    gated = activation == "swiglu"
+    gated = activation != "relu2"
+    limit, alpha, shift = _glu_form(activation, form)
     assert tuple(w_gate_up.shape) == (E, (2 if gated else 1) * ff, h) and w_gate_up.dtype == w_down.dtype == x.dtype and tuple(y.shape) == (T, h)
     assert y.dtype == torch.float32 and experts.dtype == torch.int32 and weights.dtype == torch.float32
     ints = workspace.get("moe_ints", (E + 1 + 3 * pairs,), torch.int32)
@@ -1584,15 +1606,20 @@ def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, 
     _cost(2 * pairs * h * size)
     _check(lib.mb_moe_gather(_ptr(x), _ptr(order), _ptr(weights), _ptr(xs), _ptr(token_sorted), _ptr(weight_sorted), _ptr(inv), _c_int(pairs),
                              _c_int(h), _c_int(top), _c_int(int(weight_on_input)), _stream()), "experts' inputs gathered")
-    dense = ((interleaved or not gated) and pairs >= EXPERTS_DENSE_FROM * E and use_tensor_cores and not torch.cuda.is_current_stream_capturing())
+    dense = ((interleaved or not gated or activation == "glu_capped") and pairs >= EXPERTS_DENSE_FROM * E and use_tensor_cores and not torch.cuda.is_current_stream_capturing())
     if dense:
         rows = workspace.get("moe_rows", (pairs, h), torch.float32)
         bounds = offsets.tolist()                       # the one wait on the host: how many pairs each expert got
         active = [e for e in range(E) if bounds[e + 1] > bounds[e]]
         # (while the stages of a step are being recorded everything stays on one stream, in launch order)
         lanes = min(EXPERT_STREAMS, len(active)) if launch_log is None else 1
+        gate_up = workspace.get("moe_gate_up", (pairs, 2 * ff), x.dtype) if activation == "glu_capped" else None
+
         def first_product(lo, hi, e):
-            if gated:
+            if activation == "glu_capped":        # the dense product, then the capped form over its rows (gate rows first)
+                gemm(xs[lo:hi], w_gate_up[e], gate_up[lo:hi])
+                glu_capped(gate_up[lo:hi], ff, act[lo:hi], limit, alpha, shift)
+            elif gated:
                 gemm_swiglu(xs[lo:hi], w_gate_up[e], act[lo:hi], workspace)
             else:
                 gemm_act(xs[lo:hi], w_gate_up[e], act[lo:hi], "relu2")
@@ -1629,7 +1656,8 @@ def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, 
         return
     _cost(touched * (2 if gated else 1) * ff * h * size + pairs * (h + ff) * size, (4.0 if gated else 2.0) * pairs * ff * h)
     _check(lib.mb_moe_grouped_gate_up(_ptr(xs), _ptr(w_gate_up), _ptr(offsets), _ptr(act), _c_int(pairs), _c_int(h), _c_int(ff), _c_int(E),
-                                      _c_int(int(interleaved)), _c_int(EXPERT_ACTIVATIONS[activation]), _stream()),
+                                      _c_int(int(interleaved)), _c_int(EXPERT_ACTIVATIONS[activation]), _c_float(limit), _c_float(alpha),
+                                      _c_float(shift), _stream()),
            "experts, gate|up, SwiGLU (grouped, tensor cores)" if gated else "experts, up, relu squared (grouped, tensor cores)")
     scale = None if weight_on_input else weight_sorted
     _cost(touched * ff * h * size + pairs * ff * size + 2 * pairs * h * 4, 2.0 * pairs * ff * h)
@@ -1642,3 +1670,165 @@ def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, 
                                    _c_int(pairs), _c_int(h), _c_int(ff), _c_int(E), _stream()), "experts, down (grouped, tensor cores)")
     _cost(_size(rows) + 2 * _size(y))
     _check(lib.mb_moe_combine(_ptr(rows), _ptr(inv), _ptr(None), _ptr(y), _c_int(T), _c_int(h), _c_int(top), _stream()), "experts' outputs added")
+
+
+# ---- attention over a window and pooled blocks before it (csrc/attention_pooled.cu) ------------------------------------------------
+def pool_blocks(k_cache, v_cache, k_pool, v_pool, ctx, block_table, slot_mapping, pool: int) -> None:
+    """For every token of the step that ends a block of ``pool`` positions: the means of the block's keys and of its values, as
+    the pages hold them, into the pooled rows of the page that holds the token (row ``offset // pool``)."""
+    _need_cuda(k_cache, v_cache, k_pool, v_pool, block_table, slot_mapping)
+    T = ctx.num_tokens
+    K, page_size, d, dv = k_cache.shape[1], k_cache.shape[2], k_cache.shape[3], v_cache.shape[3]
+    rows = -(-page_size // pool)
+    assert tuple(k_pool.shape[1:]) == (K, rows, d) and tuple(v_pool.shape[1:]) == (K, rows, dv) and k_pool.dtype == k_cache.dtype == v_pool.dtype
+    _cost(T * K * (d + dv) * k_cache.element_size() * (1 + 1.0 / pool))
+    _check(_lib("mb_attention_pooled").mb_pool_blocks(
+        _ptr(k_cache), _ptr(v_cache), _ptr(k_pool), _ptr(v_pool), _code(k_cache), _ptr(block_table), _c_int(block_table.shape[1]),
+        _ptr(ctx.req_index), _ptr(ctx.positions), _ptr(slot_mapping), _c_int(T), _c_int(K), _c_int(d), _c_int(dv), _c_int(page_size),
+        _c_int(pool), _c_int(rows), _stream()), "pooled blocks")
+
+
+def attention_pooled(q, k_cache, v_cache, k_pool, v_pool, out, ctx, block_table, H: int, K: int, d: int, dv: int, scale: float,
+                     softcap: float = 0.0, window: int = 0, pool: int = 0, talk: Optional[torch.Tensor] = None) -> None:
+    """Softmax attention of the step's tokens over the last ``window`` positions (0: all) and, with ``pool``, one pooled key and
+    value per block of ``pool`` positions that lies wholly before the window; scores capped by ``softcap tanh(s / softcap)``
+    where ``softcap`` > 0; ``talk`` (float32 ``[H, H]``): head ``h``'s weights are ``sum_g talk[h, g] w_g``, applied to the values
+    of its own kv head."""
+    _need_cuda(q, k_cache, v_cache, k_pool, v_pool, out, block_table, talk)
+    T = q.shape[0]
+    page_size = k_cache.shape[2]
+    assert tuple(q.shape) == (T, H * d) and tuple(out.shape) == (T, H * dv) and k_cache.dtype == q.dtype == v_cache.dtype == out.dtype
+    assert k_cache.shape[3] == d and v_cache.shape[3] == dv and (not pool or (k_pool is not None and k_pool.dtype == q.dtype))
+    assert talk is None or (talk.dtype == torch.float32 and tuple(talk.shape) == (H, H))
+    if T == 0:
+        return
+    size = q.element_size()
+    parts = ctx.workspace.get("pooled_parts", (T, H, K, dv), torch.float32) if talk is not None else None
+    if launch_log is not None:
+        _cost(T * H * (d + dv) * size, 0.0, K * (d + dv) * size, 2.0 * H * (d + (K if talk is not None else 1) * dv))
+        _pending_cost["rows"], _pending_cost["window"] = "all", window
+    rows = -(-page_size // pool) if pool else 0
+    _check(_lib("mb_attention_pooled").mb_attention_pooled(
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(k_pool), _ptr(v_pool), _ptr(parts), _ptr(out), _code(q), _ptr(block_table),
+        _c_int(block_table.shape[1]), _ptr(ctx.req_index), _ptr(ctx.positions), _ptr(ctx.seq_lens), _c_int(T), _c_int(H), _c_int(K), _c_int(d),
+        _c_int(dv), _c_int(page_size), _c_float(scale), _c_float(softcap or 0.0), _c_int(window), _c_int(pool), _c_int(rows),
+        _c_int(int(talk is not None)), _stream()), "attention (window and pooled blocks)")
+    if talk is not None:
+        _cost(_size(parts) + _size(out), 2.0 * T * H * H * dv)
+        _check(_lib("mb_attention_pooled").mb_talk_mix(_ptr(parts), _ptr(talk), _ptr(out), _code(out), _c_int(T), _c_int(H), _c_int(K), _c_int(dv),
+                                                      _stream()), "heads' weights mixed")
+
+
+# ---- a selective state space layer (csrc/ssm.cu) ---------------------------------------------------------------------------------
+def ssm_conv(rows: torch.Tensor, col: int, weight: torch.Tensor, bias: Optional[torch.Tensor], carry: torch.Tensor, ctx, slots: torch.Tensor,
+             out: torch.Tensor) -> None:
+    """``out = silu(conv(rows[:, col : col + channels]) + bias)``: a causal convolution per channel over each request's tokens,
+    ``weight`` float32 ``[channels, taps]`` whose last column meets the current token.  ``carry`` (float32 ``[slots, taps - 1,
+    channels]``, oldest first) holds a request's last inputs from earlier steps and is brought up to date."""
+    _need_cuda(rows, weight, bias, carry, slots, out)
+    T, (channels, taps) = rows.shape[0], weight.shape
+    assert tuple(out.shape) == (T, channels) and out.dtype == rows.dtype and weight.dtype == torch.float32 and col + channels <= rows.shape[1]
+    assert carry.dtype == torch.float32 and carry.is_contiguous() and tuple(carry.shape[1:]) == (taps - 1, channels) and rows.stride(1) == 1
+    _cost(2 * T * channels * rows.element_size() + _size(weight), 2.0 * T * channels * taps)
+    _check(_lib("mb_ssm").mb_ssm_conv(_ptr(rows), _c_int(rows.stride(0)), _c_int(col), _code(rows), _ptr(weight), _ptr(bias), _ptr(carry),
+                                     _ptr(ctx.req_index), _ptr(ctx.cu_tokens), _ptr(slots), _ptr(out), _c_int(T), _c_int(channels), _c_int(taps),
+                                     _stream()), "short convolution")
+    if taps > 1:
+        _cost(2 * ctx.num_requests * (taps - 1) * channels * 4)
+        _check(_lib("mb_ssm").mb_ssm_conv_carry(_ptr(rows), _c_int(rows.stride(0)), _c_int(col), _code(rows), _ptr(carry), _ptr(ctx.cu_tokens),
+                                               _ptr(slots), _c_int(ctx.num_requests), _c_int(channels), _c_int(taps), _stream()),
+               "convolution's inputs kept")
+
+
+def ssm_scan(xbc: torch.Tensor, rows: torch.Tensor, dt_col: int, dt_bias: torch.Tensor, rate_log: torch.Tensor, skip: torch.Tensor,
+             state: torch.Tensor, ctx, slots: torch.Tensor, y: torch.Tensor, heads: int, P: int, N: int, groups: int) -> None:
+    """Per head ``S <- exp(-exp(rate) dt) S + dt B x^T; y = S^T C + skip x`` over each request's tokens, ``dt = softplus(dt' +
+    dt_bias)`` with ``dt'`` of head ``h`` at ``rows[:, dt_col + h]``; ``xbc`` ``[T, heads P + 2 groups N]`` holds x | B | C;
+    ``state`` float32 ``[slots, heads, N, P]`` is read and written; ``y`` float32 ``[T, heads P]``."""
+    _need_cuda(xbc, rows, dt_bias, rate_log, skip, state, slots, y)
+    T = xbc.shape[0]
+    assert xbc.shape[1] == heads * P + 2 * groups * N and xbc.is_contiguous() and rows.dtype == xbc.dtype and rows.stride(1) == 1
+    assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, N, P)
+    assert y.dtype == torch.float32 and tuple(y.shape) == (T, heads * P) and dt_bias.dtype == rate_log.dtype == skip.dtype == torch.float32
+    R = ctx.num_requests
+    _cost(_size(xbc) + _size(y) + 2 * R * heads * N * P * 4, 6.0 * T * heads * N * P)
+    _check(_lib("mb_ssm").mb_ssm_scan(_ptr(xbc), _ptr(rows), _c_int(rows.stride(0)), _c_int(dt_col), _code(xbc), _ptr(dt_bias), _ptr(rate_log),
+                                     _ptr(skip), _ptr(state), _ptr(ctx.cu_tokens), _ptr(slots), _ptr(y), _c_int(R), _c_int(heads), _c_int(P),
+                                     _c_int(N), _c_int(groups), _stream()), "state space recurrence")
+
+
+def ssm_gate_norm(y: torch.Tensor, rows: torch.Tensor, z_col: int, weight: torch.Tensor, eps: float, parts: int, out: torch.Tensor) -> None:
+    """``out = v / rms(v) * weight`` with ``v = y silu(rows[:, z_col : z_col + n])``, the root mean square taken over each of
+    ``parts`` equal parts of the row by itself."""
+    _need_cuda(y, rows, weight, out)
+    T, n = y.shape
+    assert y.dtype == torch.float32 and weight.dtype == torch.float32 and weight.numel() == n and tuple(out.shape) == (T, n) and out.dtype == rows.dtype
+    assert rows.stride(1) == 1 and z_col + n <= rows.shape[1] and n % parts == 0
+    _cost(_size(y) + 2 * _size(out), 12.0 * T * n)
+    _check(_lib("mb_ssm").mb_ssm_gate_norm(_ptr(y), _ptr(rows), _c_int(rows.stride(0)), _c_int(z_col), _code(rows), _ptr(weight), _c_float(eps),
+                                          _ptr(out), _c_int(T), _c_int(n), _c_int(parts), _stream()), "gate, norm in parts")
+
+
+# ---- small element-wise steps (csrc/activations.cu) --------------------------------------------------------------------------------
+BIAS_ACTS = {None: 0, "gelu": 1, "gelu_tanh": 2}
+
+
+def bias_act(x: torch.Tensor, bias: Optional[torch.Tensor], activation: Optional[str]) -> None:
+    """``x <- act(x + bias)`` in place; ``activation`` None, "gelu" (erf) or "gelu_tanh"."""
+    _need_cuda(x, bias)
+    rows, n = x.shape
+    assert x.is_contiguous() and (bias is None or (bias.dtype == torch.float32 and bias.numel() == n))
+    _cost(2 * _size(x), 10.0 * x.numel())
+    _check(_lib("mb_activations").mb_bias_act(_ptr(x), _code(x), _ptr(bias), _c_int(rows), _c_int(n), _c_int(BIAS_ACTS[activation]), _stream()),
+           "bias, activation")
+
+
+def glu_capped(rows: torch.Tensor, ff: int, out: torch.Tensor, limit: float, alpha: float, shift: float, scale_col: int = -1) -> None:
+    """``out = g sigmoid(alpha g) (u + shift)`` with ``g = min(rows[:, :ff], limit)``, ``u = clamp(rows[:, ff : 2 ff], -limit, limit)``
+    (``limit`` 0: as they are); ``scale_col`` >= 0: each row times ``sigmoid(rows[:, scale_col])``."""
+    _need_cuda(rows, out)
+    T = rows.shape[0]
+    assert rows.stride(1) == 1 and rows.shape[1] >= 2 * ff and tuple(out.shape) == (T, ff) and out.dtype == rows.dtype and out.is_contiguous()
+    _cost(T * 3 * ff * rows.element_size(), 12.0 * T * ff)
+    _check(_lib("mb_activations").mb_glu_capped(_ptr(rows), _c_int(rows.stride(0)), _code(rows), _ptr(out), _c_int(T), _c_int(ff), _c_float(limit),
+                                               _c_float(alpha), _c_float(shift), _c_int(scale_col), _stream()), "capped gate")
+
+
+def head_gate(x: torch.Tensor, rows: torch.Tensor, col: int, heads: int) -> None:
+    """``x[t, a, :] *= sigmoid(rows[t, col + a])`` in place, ``x`` ``[T, heads dim]``."""
+    _need_cuda(x, rows)
+    T = x.shape[0]
+    assert x.is_contiguous() and x.shape[1] % heads == 0 and rows.dtype == x.dtype and rows.stride(1) == 1 and col + heads <= rows.shape[1]
+    _cost(2 * _size(x), 2.0 * x.numel())
+    _check(_lib("mb_activations").mb_head_gate(_ptr(x), _code(x), _ptr(rows), _c_int(rows.stride(0)), _c_int(col), _c_int(T), _c_int(heads),
+                                              _c_int(x.shape[1] // heads), _stream()), "gate per head")
+
+
+def keep_last_row(h: torch.Tensor, carry: torch.Tensor, ctx, slots: torch.Tensor) -> None:
+    """``carry[slot of request] = h[the request's last token of the step]`` (float32; ``carry`` may be a column slice of a state)."""
+    _need_cuda(h, slots)
+    T, n = h.shape
+    assert carry.is_cuda and carry.dtype == torch.float32 and carry.shape[1] == n and carry.stride(1) == 1 and h.is_contiguous()
+    _cost(ctx.num_requests * n * (4 + h.element_size()))
+    _check(_lib("mb_activations").mb_keep_last_row(_ptr(h), _code(h), _c_void_p(carry.data_ptr()), ctypes.c_longlong(carry.stride(0)),
+                                                  _ptr(ctx.cu_tokens), _ptr(slots), _c_int(ctx.num_requests), _c_int(n), _stream()), "last row kept")
+
+
+def add_row_bias(y: torch.Tensor, bias: torch.Tensor) -> None:
+    """``y[t] += bias`` over the float32 residual."""
+    _need_cuda(y, bias)
+    rows, n = y.shape
+    assert y.dtype == torch.float32 and y.is_contiguous() and bias.dtype == torch.float32 and bias.numel() == n
+    _cost(2 * _size(y))
+    _check(_lib("mb_activations").mb_add_row_bias(_ptr(y), _ptr(bias), _c_int(rows), _c_int(n), _stream()), "bias")
+
+
+def rmsnorm_cols(rows: torch.Tensor, col: int, weight: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """``out = v / rms(v) * weight`` with ``v = rows[:, col : col + n]`` (activation dtype in and out, sums in float32)."""
+    _need_cuda(rows, weight, out)
+    T, n = out.shape
+    assert rows.shape[0] == T and rows.stride(1) == 1 and col + n <= rows.shape[1] and out.dtype == rows.dtype and out.is_contiguous()
+    assert weight.dtype == torch.float32 and weight.numel() == n
+    _cost(2 * T * n * rows.element_size(), 4.0 * T * n)
+    _check(_lib("mb_activations").mb_rmsnorm_cols(_ptr(rows), _c_int(rows.stride(0)), _c_int(col), _code(rows), _ptr(weight), _c_float(eps), _ptr(out),
+                                                 _c_int(T), _c_int(n), _stream()), "rmsnorm of a column block")

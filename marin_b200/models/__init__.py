@@ -1,5 +1,5 @@
 """Architectures known to the engine.  Importing this package registers them."""
-from . import fegarax, lakulix, nirotar, qwen3  # noqa: F401  (registration)
+from . import fegarax, lakulix, nirotar, qwen3, vogunex  # noqa: F401  (registration)
 from .model import Model
 from .registry import Architecture, architecture_for, architecture_of, register_architecture, registered
 

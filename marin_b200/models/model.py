@@ -73,12 +73,14 @@ class Model:
 
     def cache_bytes_read(self, context: int, dtype: torch.dtype) -> int:
         """Bytes of the cache one decoded token of a sequence of ``context`` positions reads, over all schedule entries."""
-        total = 0
-        for entry in self.spec.schedule:
-            need = self.blocks[entry.layer].mixer.cache_need()
-            if need is not None:
-                total += need.bytes_read(context, dtype)
-        return total
+        def of(need) -> int:
+            if need is None:
+                return 0
+            if isinstance(need, (tuple, list)):                 # a mixer that keeps several things
+                return sum(of(n) for n in need)
+            return need.bytes_read(context, dtype)
+
+        return sum(of(self.blocks[entry.layer].mixer.cache_need()) for entry in self.spec.schedule)
 
     def kernel_jobs(self, dtype: torch.dtype) -> Dict[str, tuple]:
         """``{library: (sources, defines)}`` of the kernels specialised for this model's parts."""

@@ -111,29 +111,97 @@ class PolyNormMLP(FeedForward):
 
 @register_feedforward("act_mlp")
 class ActMLP(FeedForward):
-    """``down( act( x W_up^T ) )`` without a gate; ``activation`` "relu2": the square of relu, element by element."""
+    """``down( act( x W_up^T (+ b_up) ) ) (+ b_down)`` without a gate; ``activation`` "relu2": the square of relu, "gelu": the
+    exact gelu ``z (1 + erf(z / sqrt 2)) / 2``, "gelu_tanh": its tanh form, element by element.  ``bias``: both projections have
+    one (``bias_names``)."""
 
-    def __init__(self, hidden: int, intermediate: int, name: str, activation: str = "relu2", names=("up", "down")):
+    ACTIVATIONS = ("relu2", "gelu", "gelu_tanh")
+
+    def __init__(self, hidden: int, intermediate: int, name: str, activation: str = "relu2", names=("up", "down"), bias: bool = False,
+                 bias_names=("up.bias", "down.bias")):
         self.hidden, self.intermediate, self.name, self.activation = int(hidden), int(intermediate), name, activation
-        if activation not in ("relu2",):
+        if activation not in self.ACTIVATIONS:
             raise ValueError(f"act_mlp: unknown activation {activation!r}")
         self.up_name, self.down_name = (f"{name}.{n}" for n in names)
-        self.w_up = self.w_down = None
+        self.bias = bool(bias)
+        self.up_bias_name, self.down_bias_name = (f"{name}.{n}" for n in bias_names)
+        self.w_up = self.w_down = self.b_up = self.b_down = None
 
     def tensor_specs(self) -> List[TensorSpec]:
         h, i = self.hidden, self.intermediate
-        return [TensorSpec(self.up_name, (i, h)), TensorSpec(self.down_name, (h, i))]
+        specs = [TensorSpec(self.up_name, (i, h)), TensorSpec(self.down_name, (h, i))]
+        if self.bias:
+            specs += [TensorSpec(self.up_bias_name, (i,), "bias"), TensorSpec(self.down_bias_name, (h,), "bias")]
+        return specs
 
     def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
         self.w_up = rt.matrix(tensors.pop(self.up_name))
         self.w_down = rt.matrix(tensors.pop(self.down_name))
+        if self.bias:
+            self.b_up, self.b_down = rt.f32(tensors.pop(self.up_bias_name)), rt.f32(tensors.pop(self.down_bias_name))
+
+    def kernel_jobs(self, dtype) -> Dict[str, tuple]:
+        return ops.library_jobs("mb_activations")
 
     def forward(self, x, ctx, residual: torch.Tensor):
         T = x.shape[0]
         act = ctx.workspace.get("ffn_act", (T, self.intermediate), x.dtype)
         ops.stage_name = "up, activation"
-        ops.gemm_act(x, self.w_up, act, self.activation)
+        if self.activation == "relu2" and not self.bias:
+            ops.gemm_act(x, self.w_up, act, self.activation)
+        else:
+            ops.gemm(x, self.w_up, act)
+            if self.activation == "relu2":
+                ops.bias_act(act, self.b_up, None)
+                ops.relu2(act)
+            else:
+                ops.bias_act(act, self.b_up, self.activation)
         ops.stage_name = "down"
+        ops.gemm(act, self.w_down, residual, accumulate=True)
+        if self.bias:
+            ops.add_row_bias(residual, self.b_down)
+        return None
+
+
+class CappedGLU(FeedForward):
+    """``down( g sigmoid(alpha g) (u + shift) )`` with ``g = min(x W_gate^T, limit)`` and ``u = clamp(x W_up^T, -limit, limit)``, no
+    biases; ``scaled``: the result times ``sigmoid(x . w_s)``, one number per token (tensor ``[1, hidden]``): its row rides in
+    the same product as gate and up, and since the down projection is linear the number multiplies the activation's rows."""
+
+    def __init__(self, hidden: int, intermediate: int, name: str, limit: float, alpha: float, shift: float, scaled: bool, names):
+        self.hidden, self.intermediate, self.name = int(hidden), int(intermediate), name
+        self.limit, self.alpha, self.shift, self.scaled = float(limit), float(alpha), float(shift), bool(scaled)
+        self.gate_name, self.up_name, self.down_name, self.scale_name = (f"{name}.{n}" for n in names)
+        self.w_in = self.w_down = None
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        h, i = self.hidden, self.intermediate
+        specs = [TensorSpec(self.gate_name, (i, h)), TensorSpec(self.up_name, (i, h)), TensorSpec(self.down_name, (h, i))]
+        if self.scaled:
+            specs.append(TensorSpec(self.scale_name, (1, h)))
+        return specs
+
+    def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        parts = [tensors.pop(self.gate_name), tensors.pop(self.up_name)]
+        if self.scaled:
+            parts.append(tensors.pop(self.scale_name).reshape(1, self.hidden))
+            # (rows up to a multiple of 8, so that every product kernel takes the matrix)
+            parts.append(torch.zeros((-(2 * self.intermediate + 1)) % 8, self.hidden, dtype=parts[0].dtype))
+        self.w_in = rt.matrix(torch.cat(parts, dim=0))
+        self.w_down = rt.matrix(tensors.pop(self.down_name))
+
+    def kernel_jobs(self, dtype) -> Dict[str, tuple]:
+        return ops.library_jobs("mb_activations")
+
+    def forward(self, x, ctx, residual: torch.Tensor):
+        T, ff = x.shape[0], self.intermediate
+        ws = ctx.workspace
+        ops.stage_name = "shared gate|up"
+        rows = ws.get("glu_rows", (T, self.w_in.shape[0]), x.dtype)
+        ops.gemm(x, self.w_in, rows)
+        act = ws.get("glu_act", (T, ff), x.dtype)
+        ops.glu_capped(rows, ff, act, self.limit, self.alpha, self.shift, 2 * ff if self.scaled else -1)
+        ops.stage_name = "shared down"
         ops.gemm(act, self.w_down, residual, accumulate=True)
         return None
 
@@ -155,12 +223,15 @@ class RoutedExperts(FeedForward):
     ``names``: the router's (or table's) tensor and the pattern of an expert's tensors inside ``name`` (``{e}`` the expert's
     number)."""
 
-    NAMES = {"router": "router.weight", "table": "table", "gate": "experts.{e}.gate_proj.weight", "up": "experts.{e}.up_proj.weight",
-             "down": "experts.{e}.down_proj.weight", "shared_up": "shared.up", "shared_down": "shared.down"}
+    NAMES = {"router": "router.weight", "router_bias": "router.bias", "table": "table", "gate": "experts.{e}.gate_proj.weight",
+             "up": "experts.{e}.up_proj.weight", "down": "experts.{e}.down_proj.weight", "shared_gate": "shared.gate", "shared_up": "shared.up",
+             "shared_down": "shared.down", "shared_scale": "shared.scale"}
 
     def __init__(self, hidden: int, intermediate: int, experts: int, top: int, name: str, score: str = "sigmoid",
                  renormalize: bool = False, weight_on: str = "input", names=None, router: str = "learned", vocab: int = 0,
-                 activation: str = "swiglu", shared_intermediate: Optional[int] = None):
+                 activation: str = "swiglu", shared_intermediate: Optional[int] = None, router_bias: bool = False,
+                 act_limit: float = 0.0, act_alpha: float = 1.0, act_shift: float = 0.0, shared_limit: Optional[float] = None,
+                 shared_scaled: bool = False):
         self.hidden, self.intermediate, self.experts, self.top, self.name = int(hidden), int(intermediate), int(experts), int(top), name
         if not 1 <= self.top <= self.experts:
             raise ValueError(f"routed_experts: top {top} of {experts} experts")
@@ -172,12 +243,20 @@ class RoutedExperts(FeedForward):
             raise ValueError("routed_experts: a table over the token ids needs the vocabulary's size")
         self.score, self.renormalize, self.weight_on = score, bool(renormalize), weight_on
         self.routing, self.vocab, self.activation = router, int(vocab), activation
-        self.gated = activation == "swiglu"
+        self.gated = activation != "relu2"
+        # "glu_capped": g sigmoid(alpha g) (u + shift) with g <- min(g, limit), u <- clamp(u, -limit, limit); the softmax of the
+        # chosen logits alone is score "softmax" with ``renormalize`` (the common denominator cancels)
+        self.form = (float(act_limit), float(act_alpha), float(act_shift)) if activation == "glu_capped" else None
+        self.router_bias = bool(router_bias)
         self.names = dict(self.NAMES, **(names or {}))
-        self.router = self.table = self.w_gate_up = self.w_down = None
+        self.router = self.router_b = self.table = self.w_gate_up = self.w_down = None
         self.shared = None
         if shared_intermediate:
-            if self.gated:
+            if activation == "glu_capped":
+                self.shared = CappedGLU(hidden, int(shared_intermediate), name, self.form[0] if shared_limit is None else float(shared_limit),
+                                        self.form[1], self.form[2], shared_scaled,
+                                        tuple(self.names[k] for k in ("shared_gate", "shared_up", "shared_down", "shared_scale")))
+            elif self.gated:
                 self.shared = SwiGLU(hidden, int(shared_intermediate), f"{name}.shared")
             else:
                 self.shared = ActMLP(hidden, int(shared_intermediate), name, activation,
@@ -197,6 +276,8 @@ class RoutedExperts(FeedForward):
             specs.append(TensorSpec(self._n("table"), (self.vocab, self.top), "int_table", limit=self.experts))
         else:
             specs.append(TensorSpec(self._n("router"), (self.experts, h), "bias"))
+            if self.router_bias:
+                specs.append(TensorSpec(self._n("router_bias"), (self.experts,), "bias"))
         if self.shared is not None:
             specs += self.shared.tensor_specs()
         return specs
@@ -206,7 +287,7 @@ class RoutedExperts(FeedForward):
         # the dense product's SwiGLU epilogue applies, the rows alternate in blocks of 16 as it reads them, so that an expert
         # with many tokens can go to that product as it is; otherwise gate rows come first.  Without a gate: up alone, [E, ff, h].
         if self.gated:
-            self.interleaved = ops.can_fuse_swiglu(rt.dtype, self.hidden, self.intermediate)
+            self.interleaved = self.form is None and ops.can_fuse_swiglu(rt.dtype, self.hidden, self.intermediate)
             join = ops.interleave_gate_up if self.interleaved else (lambda g, u: torch.cat([g, u], dim=0))
             self.w_gate_up = rt.matrix(torch.stack([join(tensors.pop(self._n("gate", e)), tensors.pop(self._n("up", e)))
                                                     for e in range(self.experts)]))
@@ -221,6 +302,8 @@ class RoutedExperts(FeedForward):
             self.table = table.to(rt.device).contiguous()
         else:
             self.router = rt.f32(tensors.pop(self._n("router")))
+            if self.router_bias:
+                self.router_b = rt.f32(tensors.pop(self._n("router_bias")))
         if self.shared is not None:
             self.shared.load(tensors, rt)
         self.rt = rt
@@ -239,7 +322,7 @@ class RoutedExperts(FeedForward):
 
     def kernel_jobs(self, dtype) -> Dict[str, tuple]:
         jobs = ops.moe_jobs(dtype, self.hidden, self.intermediate)
-        if not self.gated:
+        if not self.gated or self.form is not None:
             jobs.update(ops.library_jobs("mb_activations"))
         return jobs
 
@@ -252,10 +335,10 @@ class RoutedExperts(FeedForward):
         if self.routing == "table":
             ops.moe_table_route(ctx.token_ids, self.table, self.experts, chosen, weights)
         else:
-            ops.moe_route(x, self.router, chosen, weights, self.score, self.renormalize)
+            ops.moe_route(x, self.router, chosen, weights, self.score, self.renormalize, self.router_b)
         ops.stage_name = "experts"
         ops.moe_experts(x, self.w_gate_up, self.w_down, chosen, weights, residual, self.weight_on == "input", ws, self.interleaved,
-                        self.activation)
+                        self.activation, self.form)
         if self.shared is not None:
             self.shared.forward(x, ctx, residual)
         return None

@@ -39,18 +39,39 @@ class PagedKV:
     #: True: a position's values are the first ``v_head_dim`` elements of its key row (a latent that keys and values share);
     #: no value pages are kept, and the mixer's view hands the key pages out as values too
     values_in_keys: bool = False
+    #: > 0: beside every position's row the cache keeps one key and one value for each whole block of ``pooled`` positions
+    #: (their means).  A block's row lies in the page that holds the block's last position, at ``(offset of that position)
+    #: // pooled``, so a page has ``ceil(page_size / pooled)`` such rows and the pooled rows need no block table of their own;
+    #: the pages of such a group are kept however old (``window`` must be None)
+    pooled: int = 0
+    #: with ``pooled``: how many of the latest positions a reader looks at one by one (what lies before them, by blocks)
+    pooled_window: int = 0
+
+    def __post_init__(self):
+        if self.pooled and self.window is not None:
+            raise ValueError("a cache that keeps pooled blocks in its pages cannot give pages back behind a window")
 
     @property
     def value_dim(self) -> int:
         return self.v_head_dim if self.v_head_dim is not None else self.head_dim
 
-    def bytes_per_token(self, dtype: torch.dtype) -> int:
-        """Bytes one position of one layer holds in the cache (keys and values)."""
-        return self.kv_heads * (self.head_dim + (0 if self.values_in_keys else self.value_dim)) * element_size(dtype)
+    def pooled_rows(self, page_size: int) -> int:
+        """Pooled rows a page of ``page_size`` positions holds (0 without pooling)."""
+        return -(-page_size // self.pooled) if self.pooled else 0
+
+    def bytes_per_token(self, dtype: torch.dtype, page_size: int = 0) -> int:
+        """Bytes one position of one layer holds in the cache (keys and values; with ``page_size`` given, its share of the
+        page's pooled rows too)."""
+        row = self.kv_heads * (self.head_dim + (0 if self.values_in_keys else self.value_dim)) * element_size(dtype)
+        if self.pooled and page_size:
+            return row + -(-row * self.pooled_rows(page_size) // page_size)
+        return row
 
     def bytes_read(self, context: int, dtype: torch.dtype) -> int:
         """Bytes one decoded token reads of a sequence of ``context`` positions."""
         kept = context if self.window is None else min(context, self.window)
+        if self.pooled and self.pooled_window:
+            kept = min(context, self.pooled_window) + max(0, context - self.pooled_window) // self.pooled
         return kept * self.bytes_per_token(dtype)
 
 
@@ -474,12 +495,23 @@ class LatentAttention(Mixer):
     ``W_uv_a (sum_j p_j c_j)``.  A run that reads another run's cache (``cache_of``) has no ``W_dkv`` of its own in use: it
     computes its queries, reads the owner's rows and applies its own ``W_uk``, ``W_uv``, sink and ``W_o``; ``own_latent=False``
     says the layer brings no ``dkv`` tensors at all.
+
+    ``q_rank``: the queries go through a latent of their own, ``q = W_q (W_qd h / rms(W_qd h) * w)`` (tensors ``q_down``,
+    ``q_norm``).  ``window``: a position sees the last so many positions only (the cache manager gives older pages back).
+    ``gate`` "head": head ``a``'s output is multiplied by ``sigmoid(W_g h)_a`` (tensor ``g`` ``[heads, hidden]``).
     """
 
-    NAMES = {"q": "q", "dkv": "dkv", "c_norm": "dkv.norm", "uk": "uk", "uv": "uv", "o": "o", "sink": "sink"}
+    NAMES = {"q": "q", "dkv": "dkv", "c_norm": "dkv.norm", "uk": "uk", "uv": "uv", "o": "o", "sink": "sink", "q_down": "q_down",
+             "q_norm": "q_down.norm", "g": "g"}
 
     def __init__(self, hidden: int, heads: int, head_dim: int, rot_dim: int, v_head_dim: int, kv_rank: int, name: str, position: PartSpec,
-                 scale: Optional[float] = None, norm_eps: float = 1e-6, sink=False, own_latent: bool = True, names=None):
+                 scale: Optional[float] = None, norm_eps: float = 1e-6, sink=False, own_latent: bool = True, names=None,
+                 q_rank: Optional[int] = None, window: Optional[int] = None, gate: Optional[str] = None):
+        if gate not in (None, "head"):
+            raise ValueError(f"latent_attention: gate {gate!r} is not one of None, 'head'")
+        self.q_rank = int(q_rank) if q_rank else None
+        self.window = int(window) if window else None
+        self.gate = gate
         self.hidden, self.heads, self.head_dim, self.rot_dim = int(hidden), int(heads), int(head_dim), int(rot_dim)
         self.v_head_dim, self.kv_rank = int(v_head_dim), int(kv_rank)
         self.name, self.norm_eps = name, float(norm_eps)
@@ -499,11 +531,17 @@ class LatentAttention(Mixer):
         return f"{self.name}.{self.names[key]}"
 
     def cache_need(self):
-        return PagedKV(1, self.row_dim, None, self.kv_rank, values_in_keys=True)
+        return PagedKV(1, self.row_dim, self.window, self.kv_rank, values_in_keys=True)
 
     def tensor_specs(self) -> List[TensorSpec]:
         h, r = self.hidden, self.kv_rank
-        specs = [TensorSpec(self._n("q"), (self.q_dim, h))]
+        if self.q_rank:
+            specs = [TensorSpec(self._n("q_down"), (self.q_rank, h)), TensorSpec(self._n("q_norm"), (self.q_rank,), "norm"),
+                     TensorSpec(self._n("q"), (self.q_dim, self.q_rank))]
+        else:
+            specs = [TensorSpec(self._n("q"), (self.q_dim, h))]
+        if self.gate:
+            specs.append(TensorSpec(self._n("g"), (self.heads, h)))
         if self.own_latent:
             specs += [TensorSpec(self._n("dkv"), (self.row_dim, h)), TensorSpec(self._n("c_norm"), (r,), "norm")]
         specs += [TensorSpec(self._n("uk"), (self.heads * self.head_dim, r)), TensorSpec(self._n("uv"), (self.o_dim, r)),
@@ -513,10 +551,21 @@ class LatentAttention(Mixer):
         return specs
 
     def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
-        parts = [tensors.pop(self._n("q"))]
+        # one product of the layer's input: the queries (or their latent) | the latent and the key part | the heads' gates
+        self.w_q = self.q_weight = None
+        if self.q_rank:
+            parts = [tensors.pop(self._n("q_down"))]
+            self.q_weight = rt.f32(tensors.pop(self._n("q_norm")))
+            self.w_q = rt.matrix(tensors.pop(self._n("q")))
+        else:
+            parts = [tensors.pop(self._n("q"))]
+        self.first = parts[0].shape[0]                  # columns of the queries (or of their latent) in that product
         if self.own_latent:
             parts.append(tensors.pop(self._n("dkv")))
             self.c_weight = rt.f32(tensors.pop(self._n("c_norm")))
+        self.gate_col = sum(p.shape[0] for p in parts)
+        if self.gate:
+            parts.append(tensors.pop(self._n("g")))
         self.w_in = rt.matrix(torch.cat(parts, dim=0))
         # per head the key expansion transposed, [heads, kv_rank, head_dim]: the queries are multiplied into the latent's space
         uk = tensors.pop(self._n("uk")).reshape(self.heads, self.head_dim, self.kv_rank)
@@ -529,18 +578,24 @@ class LatentAttention(Mixer):
         self.rt = rt
 
     def flops(self, tokens: int, pairs: int = 0) -> float:
+        w = self.window
+        if w and tokens > w and pairs == tokens * (tokens + 1) // 2:
+            pairs = w * (w + 1) // 2 + (tokens - w) * w          # one prompt from its first position: the window's pairs
+        elif w:
+            pairs = min(pairs, tokens * w)
         return super().flops(tokens, pairs) + 2.0 * pairs * self.heads * (self.row_dim + self.kv_rank)
 
     def kernel_jobs(self, dtype) -> Dict[str, tuple]:
-        jobs = ops.library_jobs("mb_attention_latent")
+        jobs = ops.library_jobs("mb_attention_latent", "mb_activations")
         jobs.update(ops.sink_attention_jobs(dtype, self.heads, 1, self.row_dim, self.kv_rank, values_in_keys=True))
         return jobs
 
     def decode_plan_key(self):
-        return ("latent_attention", self.heads, self.row_dim, self.kv_rank)
+        return ("latent_attention", self.heads, self.row_dim, self.kv_rank, self.window)
 
     def decode_plan(self, requests: int, span: int, rt: Runtime):
-        return ops.sink_decode_plan(rt.dtype, requests, self.heads, 1, self.row_dim, self.kv_rank, span, 0, 0, values_in_keys=True)
+        return ops.sink_decode_plan(rt.dtype, requests, self.heads, 1, self.row_dim, self.kv_rank, span, self.window or 0, 0,
+                                    values_in_keys=True)
 
     def forward(self, x, ctx, cache, residual: torch.Tensor):
         T = x.shape[0]
@@ -549,25 +604,196 @@ class LatentAttention(Mixer):
         if writes and not self.own_latent:
             raise ValueError("latent_attention: a layer without a latent of its own must read another run's cache")
         H, dn, dr, r, D = self.heads, self.head_dim, self.rot_dim, self.kv_rank, self.row_dim
-        w = self.w_in if writes else self.w_in[: self.q_dim]
+        if not writes and self.gate:
+            raise ValueError("latent_attention: a gated layer cannot read another run's cache")      # its columns lie behind the latent's
+        w = self.w_in if writes else self.w_in[: self.first]
         ops.stage_name = "q|dkv"
         rows = ws.get("q_dkv", (T, w.shape[0]), x.dtype)
         ops.gemm(x, w, rows)
+        heads, kv_rows = rows, None
+        if self.q_rank:
+            # the queries' latent, normed, then the queries themselves; the latent and key part stay where the first product left them
+            ops.stage_name = "q from its latent"
+            cq = ws.get("q_small", (T, self.q_rank), x.dtype)
+            ops.rmsnorm_cols(rows, 0, self.q_weight, self.norm_eps, cq)
+            heads = ws.get("q_heads", (T, self.q_dim), x.dtype)
+            ops.gemm(cq, self.w_q, heads)
+            kv_rows = rows[:, self.first:self.first + D] if writes else None
         ops.stage_name = "heads"
         q = ws.get("q_latent", (T, H * D), x.dtype)
         pos = self.position
-        ops.latent_finish(rows, q, self.c_weight, self.norm_eps, ctx.positions, pos.inv_freq, pos.rotary_dim, pos.interleaved,
-                          cache.slot_mapping, cache.k, H, dn, dr, r, writes)
+        ops.latent_finish(heads, q, self.c_weight, self.norm_eps, ctx.positions, pos.inv_freq, pos.rotary_dim, pos.interleaved,
+                          cache.slot_mapping, cache.k, H, dn, dr, r, writes, kv_rows)
         ops.stage_name = "q into the latent"
-        ops.heads_product(rows, self.q_head, dn, self.w_uk_t, q, D)
+        ops.heads_product(heads, self.q_head, dn, self.w_uk_t, q, D)
         mixed = ws.get("latent_out", (T, H * r), x.dtype)
         ops.stage_name = "attention, latent"
         plans = ctx.decode_plans
-        ops.attention_sink(q, cache.k, cache.k, mixed, ctx, cache.block_table, H, 1, D, r, self.scale, 0, 0, self.sink, None,
+        ops.attention_sink(q, cache.k, cache.k, mixed, ctx, cache.block_table, H, 1, D, r, self.scale, self.window or 0, 0, self.sink, None,
                            plans.get(self.decode_plan_key()) if plans else None, self.sink_logits)
         ops.stage_name = "v from the latent"
         out = ws.get("attn_out", (T, self.o_dim), x.dtype)
         ops.heads_product(mixed, r, r, self.w_uv, out, self.v_head_dim)
+        if self.gate:
+            ops.stage_name = "gate"
+            ops.head_gate(out, rows, self.gate_col, H)
         ops.stage_name = "o"
         ops.gemm(out, self.w_o, residual, accumulate=True)
         return None
+
+
+@register_mixer("pooled_attention")
+class PooledAttention(Mixer):
+    """Causal grouped-query softmax attention over a window of single positions and, before it, pooled blocks.
+
+    ``q, k, v = x W^T (+ b)`` (``bias``); value heads ``v_head_dim`` wide; the rotation comes from ``position``; ``qk_norm``: q
+    and k are divided by their root mean square per head, without a weight (before or after a rotation in pairs it is the same
+    number).  Score ``q . k * scale``, then ``softcap tanh(s / softcap)`` where ``softcap`` is given.  Position ``i`` sees the
+    positions ``j`` with ``0 <= i - j < window`` and, with ``pool`` = P, one key and one value for every block ``b`` of P
+    positions with ``b P + P - 1 <= i - window``: the means of the block's keys and values as the cache holds them.  Positions
+    that have left the window and whose block is not complete behind it are not seen.  One softmax over both kinds.  ``talk``: a
+    learned matrix ``[heads, heads]`` mixes the heads' softmax weights, ``w'_h = sum_g talk[h, g] w_g``, and head ``h`` applies
+    ``w'_h`` to the values of its own kv head.  Without ``window`` every earlier position is seen and ``pool`` has no effect.
+    The cache keeps every position's key and value (the pooled rows live in the pages, see ``PagedKV.pooled``).
+    """
+
+    NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight", "q_bias": "q_proj.bias",
+             "k_bias": "k_proj.bias", "v_bias": "v_proj.bias", "talk": "talk"}
+
+    def __init__(self, hidden: int, heads: int, kv_heads: int, head_dim: int, name: str, position: PartSpec, v_head_dim: Optional[int] = None,
+                 scale: Optional[float] = None, bias: bool = False, qk_norm: bool = False, norm_eps: float = 1e-6, window: Optional[int] = None,
+                 pool: Optional[int] = None, softcap: Optional[float] = None, talk: bool = False, names=None):
+        self.hidden, self.heads, self.kv_heads, self.head_dim = int(hidden), int(heads), int(kv_heads), int(head_dim)
+        if self.heads % self.kv_heads != 0:
+            raise ValueError(f"{heads} heads cannot share {kv_heads} kv heads evenly")
+        self.v_head_dim = int(v_head_dim) if v_head_dim is not None else self.head_dim
+        self.name, self.bias, self.qk_norm, self.norm_eps = name, bool(bias), bool(qk_norm), float(norm_eps)
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.head_dim)
+        self.window = int(window) if window else None
+        self.pool = int(pool) if pool and self.window else None
+        self.softcap = float(softcap) if softcap else None
+        self.talk = bool(talk)
+        self.position = lookup("position", position.kind)(**position.params)
+        self.names = dict(self.NAMES, **(names or {}))
+        self.q_dim, self.k_dim = self.heads * self.head_dim, self.kv_heads * self.head_dim
+        self.v_dim, self.o_dim = self.kv_heads * self.v_head_dim, self.heads * self.v_head_dim
+        self.w_in = self.w_o = self.q_b = self.k_b = self.v_b = self.talk_w = self.ones = None
+
+    def _n(self, key: str) -> str:
+        return f"{self.name}.{self.names[key]}"
+
+    def cache_need(self):
+        if self.pool:
+            return PagedKV(self.kv_heads, self.head_dim, None, self.v_head_dim, pooled=self.pool, pooled_window=self.window)
+        return PagedKV(self.kv_heads, self.head_dim, self.window, self.v_head_dim)
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        h = self.hidden
+        specs = [TensorSpec(self._n("q"), (self.q_dim, h)), TensorSpec(self._n("k"), (self.k_dim, h)),
+                 TensorSpec(self._n("v"), (self.v_dim, h)), TensorSpec(self._n("o"), (h, self.o_dim))]
+        if self.bias:
+            specs += [TensorSpec(self._n("q_bias"), (self.q_dim,), "bias"), TensorSpec(self._n("k_bias"), (self.k_dim,), "bias"),
+                      TensorSpec(self._n("v_bias"), (self.v_dim,), "bias")]
+        if self.talk:
+            specs.append(TensorSpec(self._n("talk"), (self.heads, self.heads), "bias", 1.0 / self.heads))
+        return specs
+
+    def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        self.w_in = rt.matrix(torch.cat([tensors.pop(self._n(p)) for p in "qkv"], dim=0))
+        self.w_o = rt.matrix(tensors.pop(self._n("o")))
+        if self.bias:
+            self.q_b, self.k_b, self.v_b = (rt.f32(tensors.pop(self._n(f"{p}_bias"))) for p in "qkv")
+        if self.talk:
+            self.talk_w = rt.f32(tensors.pop(self._n("talk")))
+        if self.qk_norm:
+            self.ones = torch.ones(self.head_dim, device=rt.device, dtype=torch.float32)
+        self.position.load(tensors, rt)
+        self.rt = rt
+
+    def flops(self, tokens: int, pairs: int = 0) -> float:
+        w = self.window
+        if w and tokens > 0:
+            each = pairs / tokens                               # keys a token would see without the window, on average
+            pairs = int(tokens * (min(each, w) + (max(0.0, each - w) / self.pool if self.pool else 0.0)))
+        values = (self.kv_heads if self.talk else 1) * self.v_head_dim
+        return super().flops(tokens, pairs) + 2.0 * pairs * self.heads * (self.head_dim + values)
+
+    def kernel_jobs(self, dtype) -> Dict[str, tuple]:
+        return ops.library_jobs("mb_attention_sink", "mb_attention_pooled")
+
+    def forward(self, x, ctx, cache, residual: torch.Tensor):
+        T = x.shape[0]
+        ws = ctx.workspace
+        writes = cache.owner
+        w = self.w_in if writes else self.w_in[: self.q_dim]
+        ops.stage_name = "q|k|v"
+        rows = ws.get("qkv", (T, w.shape[0]), x.dtype)
+        ops.gemm(x, w, rows)
+        ops.stage_name = "heads"
+        q = ws.get("q", (T, self.q_dim), x.dtype)
+        pos = self.position
+        ops.qkv_finish(rows, q, self.q_b, self.k_b, self.v_b, "head" if self.qk_norm else None, self.ones, self.ones, self.norm_eps,
+                       ctx.positions, pos.inv_freq, pos.rotary_dim, pos.magnitude, cache.slot_mapping, cache.k, cache.v, None, None, None,
+                       self.heads, self.kv_heads, self.head_dim, self.v_head_dim, writes, pos.interleaved)
+        if self.pool and writes:
+            ops.stage_name = "pooled blocks"
+            ops.pool_blocks(cache.k, cache.v, cache.k_pool, cache.v_pool, ctx, cache.block_table, cache.slot_mapping, self.pool)
+        out = ws.get("attn_out", (T, self.o_dim), x.dtype)
+        ops.stage_name = "attention"
+        ops.attention_pooled(q, cache.k, cache.v, cache.k_pool, cache.v_pool, out, ctx, cache.block_table, self.heads, self.kv_heads,
+                             self.head_dim, self.v_head_dim, self.scale, self.softcap or 0.0, self.window or 0, self.pool or 0, self.talk_w)
+        ops.stage_name = "o"
+        ops.gemm(out, self.w_o, residual, accumulate=True)
+        return None
+
+
+@register_mixer("token_shifted")
+class ShiftedMixer(Mixer):
+    """Any mixer behind a token shift: what the inner mixer reads is ``h + (h' - h) * mu`` element by element, ``h'`` the row the
+    token before brought (as it was before its own shift; zeros before a sequence's first token) and ``mu`` a learned vector
+    (tensor ``tensor``, a full name).  The last row a request has brought is part of its state, beside whatever the inner mixer
+    keeps: ``cache_need`` answers both, the view is the pair of their views."""
+
+    def __init__(self, hidden: int, tensor: str, inner: PartSpec, name: str):
+        self.hidden, self.tensor, self.name = int(hidden), tensor, name
+        self.inner = lookup("mixer", inner.kind)(name=name, **inner.params)
+        self.capturable = getattr(self.inner, "capturable", True)
+        self.mu = None
+
+    def cache_need(self):
+        return (StateNeed((self.hidden,), torch.float32), self.inner.cache_need())
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        return [TensorSpec(self.tensor, (self.hidden,), "bias", 0.5)] + self.inner.tensor_specs()
+
+    def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        self.mu = rt.f32(tensors.pop(self.tensor)).reshape(1, self.hidden)
+        self.inner.load(tensors, rt)
+        self.rt = rt
+
+    def bytes_read(self, tokens: int, dtype) -> int:
+        return self.hidden * 4 + self.inner.bytes_read(tokens, dtype)
+
+    def flops(self, tokens: int, pairs: int = 0) -> float:
+        return self.inner.flops(tokens, pairs)
+
+    def kernel_jobs(self, dtype) -> Dict[str, tuple]:
+        jobs = ops.library_jobs("mb_activations")
+        jobs.update(self.inner.kernel_jobs(dtype))
+        return jobs
+
+    def decode_plan_key(self):
+        return self.inner.decode_plan_key()
+
+    def decode_plan(self, requests: int, span: int, rt: Runtime):
+        return self.inner.decode_plan(requests, span, rt)
+
+    def forward(self, x, ctx, cache, residual: torch.Tensor):
+        last, inner_cache = cache
+        if not last.owner:
+            raise ValueError("token_shifted: a run that reads another run's cache would share its last row too")
+        ops.stage_name = "token shift"
+        shifted = ctx.workspace.get("shifted", (1,) + tuple(x.shape), x.dtype)
+        ops.shift_mix(x, last.state, ctx, last.slots, self.mu, shifted)
+        ops.keep_last_row(x, last.state, ctx, last.slots)
+        return self.inner.forward(shifted[0], ctx, inner_cache, residual)

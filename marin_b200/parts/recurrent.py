@@ -173,3 +173,86 @@ class WKV(Mixer):
         ops.stage_name = "o"
         ops.gemm(out, self.w_o, residual, accumulate=True)
         return None
+
+
+@register_mixer("mamba2")
+class Mamba2(Mixer):
+    """A selective state space layer with one decay per head and token (Mamba-2: Dao, Gu, "Transformers are SSMs: Generalized
+    Models and Efficient Algorithms Through Structured State Space Duality").
+
+    With ``inner = heads * v_head_dim``, N = ``state`` and G = ``groups``, ``W_in h`` is laid out as ``z [inner] | x [inner] |
+    B [G N] | C [G N] | dt [heads]``.  x, B and C together pass a causal convolution per channel of ``taps`` taps (weight
+    ``[channels, taps]`` whose last column meets the current token, a bias) and silu.  ``dt <- softplus(dt + dt_bias)``; per
+    head (head ``a`` uses group ``a // (heads / G)``): ``S_t = exp(-exp(rate_a) dt) S_(t-1) + dt B_t x_t^T`` (``N x v_head_dim``),
+    ``y_t = S_t^T C_t + skip_a x_t``.  ``y`` (heads side by side) times ``silu(z)`` is divided by its root mean square in
+    ``norm_groups`` equal parts (each by its own), times a weight, then ``W_o`` into the residual.  A request's state is the
+    matrices of all heads (float32, zero at first) and the convolution's last ``taps - 1`` inputs: two slots' worth, kept as
+    two needs."""
+
+    NAMES = {"in": "in_proj", "conv": "conv", "conv_bias": "conv.bias", "dt_bias": "dt_bias", "rate": "A_log", "skip": "D", "norm": "norm",
+             "o": "out_proj"}
+
+    def __init__(self, hidden: int, heads: int, v_head_dim: int, state: int, groups: int, taps: int, name: str, norm_groups: int = 1,
+                 norm_eps: float = 1e-6, names=None):
+        self.hidden, self.heads, self.v_head_dim, self.state = int(hidden), int(heads), int(v_head_dim), int(state)
+        self.groups, self.taps, self.norm_groups = int(groups), int(taps), int(norm_groups)
+        self.name, self.norm_eps = name, float(norm_eps)
+        if self.heads % self.groups != 0:
+            raise ValueError(f"mamba2: {heads} heads cannot share {groups} groups evenly")
+        self.inner = self.heads * self.v_head_dim
+        if self.inner % self.norm_groups != 0:
+            raise ValueError(f"mamba2: the norm's {norm_groups} parts do not divide {self.inner}")
+        if self.state > 256 or self.taps > 64:
+            raise ValueError("mamba2: a state above 256 rows or more than 64 taps is not supported")
+        self.channels = self.inner + 2 * self.groups * self.state
+        self.in_dim = 2 * self.inner + 2 * self.groups * self.state + self.heads
+        self.names = dict(self.NAMES, **(names or {}))
+
+    def _n(self, key: str) -> str:
+        return f"{self.name}.{self.names[key]}"
+
+    def cache_need(self):
+        return (StateNeed((self.heads, self.state, self.v_head_dim), torch.float32),
+                StateNeed((max(self.taps - 1, 1), self.channels), torch.float32))
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        h = self.hidden
+        return [TensorSpec(self._n("in"), (self.in_dim, h)), TensorSpec(self._n("conv"), (self.channels, self.taps), "bias", 1.0 / self.taps),
+                TensorSpec(self._n("conv_bias"), (self.channels,), "bias"), TensorSpec(self._n("dt_bias"), (self.heads,), "bias"),
+                TensorSpec(self._n("rate"), (self.heads,), "bias"), TensorSpec(self._n("skip"), (self.heads,), "bias", 1.0),
+                TensorSpec(self._n("norm"), (self.inner,), "norm"), TensorSpec(self._n("o"), (h, self.inner))]
+
+    def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        self.w_in = rt.matrix(tensors.pop(self._n("in")))
+        self.conv_w, self.conv_b = rt.f32(tensors.pop(self._n("conv"))), rt.f32(tensors.pop(self._n("conv_bias")))
+        self.dt_bias, self.rate, self.skip = (rt.f32(tensors.pop(self._n(k))) for k in ("dt_bias", "rate", "skip"))
+        self.norm_w = rt.f32(tensors.pop(self._n("norm")))
+        self.w_o = rt.matrix(tensors.pop(self._n("o")))
+        self.rt = rt
+
+    def flops(self, tokens: int, pairs: int = 0) -> float:
+        return super().flops(tokens, pairs) + tokens * (6.0 * self.heads * self.state * self.v_head_dim + 2.0 * self.channels * self.taps)
+
+    def kernel_jobs(self, dtype) -> Dict[str, tuple]:
+        return ops.library_jobs("mb_ssm")
+
+    def forward(self, x, ctx, cache, residual: torch.Tensor):
+        T = x.shape[0]
+        ws = ctx.workspace
+        matrices, kept = cache
+        ops.stage_name = "z|x|B|C|dt"
+        rows = ws.get("ssm_rows", (T, self.in_dim), x.dtype)
+        ops.gemm(x, self.w_in, rows)
+        ops.stage_name = "convolution"
+        xbc = ws.get("ssm_xbc", (T, self.channels), x.dtype)
+        ops.ssm_conv(rows, self.inner, self.conv_w, self.conv_b, kept.state if self.taps > 1 else kept.state[:, :0], ctx, kept.slots, xbc)
+        ops.stage_name = "recurrence"
+        y = ws.get("ssm_y", (T, self.inner), torch.float32)
+        ops.ssm_scan(xbc, rows, self.inner + self.channels, self.dt_bias, self.rate, self.skip, matrices.state, ctx, matrices.slots, y,
+                     self.heads, self.v_head_dim, self.state, self.groups)
+        ops.stage_name = "gate, norm"
+        out = ws.get("ssm_out", (T, self.inner), x.dtype)
+        ops.ssm_gate_norm(y, rows, 0, self.norm_w, self.norm_eps, self.norm_groups, out)
+        ops.stage_name = "o"
+        ops.gemm(out, self.w_o, residual, accumulate=True)
+        return None
