@@ -172,6 +172,15 @@ def capped_expert(h: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, down: t
     return (g * torch.sigmoid(1.702 * g) * (u + 1.0)) @ down.T
 
 
+def router_margins(h: torch.Tensor, t: Dict[str, torch.Tensor], name: str, mlp: dict) -> torch.Tensor:
+    """Per row, how far the last chosen expert's logit lies above the first one not chosen (infinite where all are chosen)."""
+    E, top = mlp["router"]["experts"], mlp["router"]["top"]
+    if top >= E:
+        return torch.full((h.shape[0],), float("inf"), dtype=F)
+    z = torch.sort(h @ t[f"{name}.router"].T + t[f"{name}.router.b"], dim=1, descending=True).values
+    return z[:, top - 1] - z[:, top]
+
+
 def routed_mlp(h: torch.Tensor, t: Dict[str, torch.Tensor], name: str, mlp: dict) -> torch.Tensor:
     """The ``top`` experts with the largest router logits, weighted by the softmax over those logits alone, plus a shared
     expert times a sigmoid of the token."""
@@ -195,10 +204,19 @@ def routed_mlp(h: torch.Tensor, t: Dict[str, torch.Tensor], name: str, mlp: dict
 MIXERS = {"attention": pooled_window_attention, "latent_attention": latent_attention, "mamba2": mamba2}
 
 
-def forward(config: dict, tensors: Dict[str, torch.Tensor], tokens: List[int], residuals: Optional[list] = None) -> torch.Tensor:
-    """Logits ``[T, vocab]`` of one sequence from its first position; ``residuals`` collects the stream after every layer."""
+def read_weights(path: str) -> Dict[str, torch.Tensor]:
+    from safetensors.torch import load_file
+    import os
+
+    return {k: v.to(F) for k, v in load_file(os.path.join(path, "model.safetensors")).items()}
+
+
+def forward(config: dict, tensors: Dict[str, torch.Tensor], tokens: List[int], residuals: Optional[list] = None,
+            margins: Optional[list] = None) -> torch.Tensor:
+    """Logits ``[T, vocab]`` of one sequence from its first position; ``residuals`` collects the stream after every layer,
+    ``margins`` every routed layer's ``router_margins``."""
     eps = config["norm"]["eps"]
-    x = tensors["embed"][torch.tensor(tokens)] * config["embedding"]["scale"]
+    x = tensors["embed"][torch.tensor(tokens)] * (config.get("embedding") or {}).get("scale", 1.0)
     for i, layer in enumerate(config["layers"]):
         p = f"l{layer.get('weights_of', i) if layer.get('weights_of') is not None else i}"
         h = rms_norm(x, tensors[f"{p}.norm1"], eps)
@@ -208,6 +226,8 @@ def forward(config: dict, tensors: Dict[str, torch.Tensor], tokens: List[int], r
         mlp = layer.get("mlp")
         if mlp is not None:
             h = rms_norm(x, tensors[f"{p}.norm2"], eps)
+            if margins is not None and mlp["kind"] != "dense":
+                margins.append(router_margins(h, tensors, f"{p}.mlp", mlp))
             x = x + (dense_mlp(h, tensors, f"{p}.mlp") if mlp["kind"] == "dense" else routed_mlp(h, tensors, f"{p}.mlp", mlp))
         if residuals is not None:
             residuals.append(x.clone())

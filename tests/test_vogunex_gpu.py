@@ -1,0 +1,586 @@
+"""Vogunex on the GPU against the plain implementation (``plain_vogunex``, float64 on the CPU): every mechanism alone, then
+whole models under every way of cutting the work: each request alone and whole; most of it in one step and the rest one
+token at a time (eagerly and from captured graphs); portions of changing size down to two tokens; mixed batches of unequal
+requests with so few pages that they are used again; greedy generation through the engine's entry point and scheduler; and
+the trace replay as a user runs it.
+
+Tolerances.  float32: |diff| <= 2e-4 (1 + |ref|), the plain result being float64.  bfloat16: the root mean square of the
+difference over a row at most 0.06 of the reference's own root mean square and 0.03 on average.  In whole models this holds
+for a request's rows before the first one whose choice of experts is a close call in float64 (a router margin under 0.1: in
+16 bits it may fall the other way, and the states and keys behind it carry that on to every later row); of the rows from
+there on the median must still be within 0.06.
+"""
+import json
+import math
+import os
+import random
+import subprocess
+import sys
+from types import SimpleNamespace
+
+import numpy as np
+import pytest
+import torch
+
+import plain_vogunex as plain
+from helpers import mixed_schedule, portions, random_prompt, run_mixed, run_portions, run_whole
+from vogunex_models import CONFIGS, PAGE, _attn, _latent, _moe, _ssm, make_model_dir
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device(os.environ.get("MARIN_B200_TEST_DEVICE", "cuda:0"))
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+DTYPES = ["float32", "bfloat16"]
+LENGTHS = {"A": {"a": 37, "b": 9, "c": 150, "d": 1, "e": 66, "f": 41, "g": 27},
+           "B": {"a": 140, "b": 2, "c": 65, "d": 260, "e": 31, "f": 129, "g": 200},
+           "C": {"a": 100, "b": 1, "c": 190, "d": 17, "e": 64}}
+
+
+def close(got, want, dtype, what="", loose_rows=0.0, safe=None):
+    got, want = got.detach().double().cpu(), want.double()
+    assert got.shape == want.shape, (what, got.shape, want.shape)
+    if safe is not None and safe < got.shape[0] and not str(dtype).endswith("float32"):
+        scale = want.pow(2).mean().sqrt()
+        rest = (got[safe:] - want[safe:]).reshape(got.shape[0] - safe, -1).pow(2).mean(dim=1).sqrt() / scale
+        assert rest.median() <= 0.06, f"{what}: behind the first close call the median row is {rest.median():.3e} off"
+        got, want = got[:safe], want[:safe]
+        if safe == 0:
+            return
+    if str(dtype).endswith("float32"):
+        bad = (got - want).abs() > 2e-4 * (1 + want.abs())
+        if bad.any():
+            first = int(torch.nonzero(bad.reshape(bad.shape[0], -1).any(dim=1))[0])
+            raise AssertionError(f"{what}: first wrong row {first} of {got.shape[0]}, max err {(got - want).abs().max():.3e}")
+    else:
+        scale = want.pow(2).mean().sqrt()
+        rows = (got - want).reshape(got.shape[0], -1).pow(2).mean(dim=1).sqrt() / scale
+        over = rows > 0.06
+        allowed = int(math.ceil(loose_rows * rows.numel()))
+        if int(over.sum()) > allowed or (bool((~over).any()) and rows[~over].mean() > 0.03):
+            raise AssertionError(f"{what}: {int(over.sum())} of {rows.numel()} rows beyond 0.06 (first {int(torch.nonzero(over)[0]) if over.any() else -1}, "
+                                 f"max {rows.max():.3e}), mean of the others {rows[~over].mean():.3e}")
+
+
+def torch_dtype(name):
+    return torch.float32 if name == "float32" else torch.bfloat16
+
+
+def runtime(dtype):
+    from marin_b200.parts import Runtime
+    return Runtime(DEV, torch_dtype(dtype))
+
+
+def bf(t):
+    return t.to(torch.bfloat16)
+
+
+def harness(needs, rt, page=8, pages=80, ctx_len=2048):
+    from marin_b200.cache import CacheManager
+    from marin_b200.engine import Runner
+
+    cache = CacheManager(list(needs), [None] * len(needs), page, pages, 4)
+    cache.allocate(rt.device, rt.dtype)
+    return Runner(SimpleNamespace(spec=SimpleNamespace(vocab_size=1 << 30)), cache, rt, ctx_len)
+
+
+def feed(parts, runner, x, cuts, req="r", mixer=True):
+    """Runs ``x`` [T, hidden] through the parts (each on the same input, mixers with their view of the cache) in portions
+    ``cuts``; returns what each added to a zero residual."""
+    from marin_b200.engine import StepEntry
+
+    runner.begin(req)
+    got, at = [[] for _ in parts], 0
+    for n in cuts:
+        runner.cache.reserve(req, at + n)
+        ctx = runner.build_context([StepEntry(req, [0] * n, [])])
+        for i, part in enumerate(parts):
+            residual = torch.zeros(n, x.shape[1], device=DEV)
+            rows = x[at:at + n].to(DEV).contiguous()
+            if mixer:
+                part.forward(rows, ctx, runner.views.view(i, ctx), residual)
+            else:
+                part.forward(rows, ctx, residual)
+            got[i].append(residual.cpu())
+        runner.cache.commit(req, at + n)
+        at += n
+    runner.end(req)
+    assert at == x.shape[0]
+    return [torch.cat(g) for g in got]
+
+
+def mat(g, r, c, gain=1.0):
+    return torch.randn(r, c, generator=g) * gain / math.sqrt(c)
+
+
+def build_mixer(kind, m, hidden, eps, rt, weights, shift=None):
+    """The registered part of a layer's mixer (with the token shift in front of it if ``shift`` names its tensor), loaded."""
+    from marin_b200.config.vogunex import _mixer as parse
+    from marin_b200.models.vogunex import _mixer as spec_of
+    from marin_b200.parts import lookup
+    from marin_b200.parts.spec import PartSpec
+
+    spec = spec_of(kind, parse(kind, m, ""), hidden, eps)
+    if shift is not None:
+        spec = PartSpec("token_shifted", {"hidden": hidden, "tensor": shift, "inner": spec})
+    part = lookup("mixer", spec.kind)(name="m.mix", **spec.params)
+    part.load({k: v.clone() for k, v in weights.items()}, rt)
+    return part
+
+
+def cuts_for(T):
+    return [[T], [max(T - 40, 1)] + [1] * (T - max(T - 40, 1)), portions(T, [7, 2, 13, 3, 2, 5]), portions(T, [2])]
+
+
+# ---- attention over a window and pooled blocks, alone ------------------------------------------------------------------------
+
+def attention_weights(hidden, m, seed, same_qk=False):
+    g = torch.Generator().manual_seed(seed)
+    H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    w = {"m.mix.q": mat(g, H * d, hidden, 2.0), "m.mix.k": mat(g, G * d, hidden, 2.0), "m.mix.v": mat(g, G * dv, hidden),
+         "m.mix.o": mat(g, hidden, H * dv), "m.mix.q.b": 0.5 * torch.randn(H * d, generator=g), "m.mix.k.b": 0.5 * torch.randn(G * d, generator=g),
+         "m.mix.v.b": 0.3 * torch.randn(G * dv, generator=g), "m.mix.talk": torch.eye(H) + 0.3 * torch.randn(H, H, generator=g)}
+    if same_qk:
+        assert H == G
+        w["m.mix.k"], w["m.mix.k.b"] = w["m.mix.q"].clone(), w["m.mix.q.b"].clone()
+    return {k: bf(v) for k, v in w.items()}
+
+
+ATTENTIONS = [
+    _attn(4, 2, 12, 10, 0.3, size=9, pool=3, rot={"base": 100.0, "dims": 6}, softcap=5.0),
+    _attn(8, 2, 64, 64, 0.125, size=40, pool=8, rot={"base": 10000.0, "dims": 32}, softcap=30.0),
+    _attn(2, 2, 32, 16, 0.2, size=3, pool=5, rot={"base": 50.0, "dims": 32}),              # a window shorter than a block
+    _attn(3, 1, 16, 24, 0.25, size=6, pool=1),                                            # every position a block of its own
+    _attn(2, 1, 16, 16, 0.25, size=11),                                                   # a window and nothing before it
+    _attn(4, 4, 8, 8, 0.35),                                                              # every earlier position
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m", ATTENTIONS, ids=lambda m: f"h{m['heads']}k{m['kv_heads']}d{m['dim']}w{(m.get('mask') or {}).get('size')}p{(m.get('mask') or {}).get('pool')}")
+def test_pooled_attention_alone(dtype, m):
+    """Every position has edges of its own (the first tokens, the window's, a block that has just become whole), so comparing all
+    positions under all cuts covers them in prompts and in decoding; pages of eight against pools of 1, 3, 5 and 8."""
+    rt, hidden, T = runtime(dtype), 48, 97
+    w = attention_weights(hidden, m, 5)
+    x = bf(torch.randn(T, hidden, generator=torch.Generator().manual_seed(6)))
+    want = plain.pooled_window_attention(x.double(), {k: v.double() for k, v in w.items()}, "m.mix", m, 1e-5)
+    part = build_mixer("attention", m, hidden, 1e-5, rt, w)
+    for cuts in cuts_for(T):
+        runner = harness([part.cache_need()], rt, page=8)
+        close(feed([part], runner, x.to(rt.dtype), cuts)[0], want, dtype, f"cuts {cuts[:4]}")
+        runner.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("back", [0, 8, 9, 10, 13, 14, 15, 16, 17, 130, 131, 132, 135, 136, 137, 250])
+def test_one_key_stands_out(dtype, back):
+    """The last token's query meets its own direction in the key ``back`` positions before it and nearly nothing elsewhere; the
+    values there are large.  With a window of 9 and blocks of 4 over 270 positions that key is inside the window, has just left
+    it into a block that is not whole yet (and must not be seen), or lies in a block far back, right at or beside a block's and
+    a page's border: an output that misses it, or sees what it must not, is wrong by far more than any tolerance."""
+    rt, hidden, T = runtime(dtype), 32, 270
+    m = _attn(2, 2, 16, 16, 1.0, size=9, pool=4)
+    g = torch.Generator().manual_seed(back)
+    w = attention_weights(hidden, m, 3, same_qk=True)
+    w["m.mix.talk"] = bf(torch.tensor([[1.0, 0.25], [-0.5, 1.0]]))
+    w["m.mix.q.b"] = w["m.mix.k.b"] = bf(torch.zeros(32))
+    x = 0.05 * torch.randn(T, hidden, generator=g)
+    u = torch.randn(hidden, generator=g)
+    x[T - 1] = u
+    x[T - 1 - back] = 3.0 * u
+    x = bf(x)
+    want = plain.pooled_window_attention(x.double(), {k: v.double() for k, v in w.items()}, "m.mix", m, 1e-5)
+    part = build_mixer("attention", m, hidden, 1e-5, rt, w)
+    for cuts in ([T], [T - 1, 1], [T - 20] + [1] * 20, portions(T, [16, 2, 5])):
+        runner = harness([part.cache_need()], rt, page=8)
+        got = feed([part], runner, x.to(rt.dtype), cuts)[0]
+        close(got[-24:], want[-24:], dtype, f"back {back}, cuts {cuts[:3]}")
+
+
+def test_pooled_rows_live_in_the_pages_and_are_given_back_with_them():
+    """Pages, their pooled rows and state slots are handed to the next request: a second request in the places of a first one
+    gets what it gets alone in a fresh cache."""
+    rt, hidden = runtime("float32"), 48
+    m = ATTENTIONS[0]
+    w = attention_weights(hidden, m, 8)
+    part = build_mixer("attention", m, hidden, 1e-5, rt, w, shift=None)
+    need = part.cache_need()
+    assert need.pooled == 3 and need.window is None and need.pooled_rows(8) == 3 and need.pooled_rows(2) == 1
+    g = torch.Generator().manual_seed(2)
+    xs = [bf(torch.randn(n, hidden, generator=g)).float() for n in (61, 50, 64)]
+    runner = harness([need], rt, page=8, pages=8)
+    outs = [feed([part], runner, x, portions(x.shape[0], [9, 1, 4]), req=f"r{i}")[0] for i, x in enumerate(xs)]
+    assert runner.cache.groups[0].pool.num_held == 0
+    runner.cache.check()
+    for x, got in zip(xs, outs):
+        fresh = harness([need], rt, page=8, pages=8)
+        assert torch.equal(feed([part], fresh, x, [x.shape[0]])[0], got)
+
+
+# ---- token shift --------------------------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_token_shift_carries_the_last_row_across_steps(dtype):
+    rt, hidden, T = runtime(dtype), 48, 40
+    m = ATTENTIONS[4]
+    w = attention_weights(hidden, m, 9)
+    w["l.shift"] = bf(torch.rand(hidden, generator=torch.Generator().manual_seed(1)))
+    x = bf(torch.randn(T, hidden, generator=torch.Generator().manual_seed(4)))
+    w64 = {k: v.double() for k, v in w.items()}
+    want = plain.pooled_window_attention(plain.token_shift(x.double(), w64["l.shift"]), w64, "m.mix", m, 1e-5)
+    part = build_mixer("attention", m, hidden, 1e-5, rt, w, shift="l.shift")
+    for cuts in ([T], [1] * T, portions(T, [2]), portions(T, [5, 1, 1, 9])):
+        runner = harness([part.cache_need()], rt, page=4)
+        close(feed([part], runner, x.to(rt.dtype), cuts)[0], want, dtype, f"cuts {cuts[:4]}")
+    # a slot that is used again starts from zeros
+    runner = harness([part.cache_need()], rt, page=4)
+    for req in ("a", "b"):
+        close(feed([part], runner, x.to(rt.dtype), [7, T - 7], req=req)[0], want, dtype, req)
+
+
+# ---- attention over a shared latent: queries through a latent, a window, a gate per head ---------------------------------------
+
+def latent_weights(hidden, m, seed):
+    g = torch.Generator().manual_seed(seed)
+    H, d, dv, r, dr, qr = m["heads"], m["dim"], m["vdim"], m["kv_rank"], m["rot_dim"], m["q_rank"]
+    w = {"m.mix.dq": mat(g, qr, hidden, 2.0), "m.mix.dq.norm": 1.2 + 0.3 * torch.randn(qr, generator=g), "m.mix.uq": mat(g, H * (d + dr), qr, 2.0),
+         "m.mix.dkv": mat(g, r + dr, hidden, 2.0), "m.mix.dkv.norm": 1.2 + 0.3 * torch.randn(r, generator=g),
+         "m.mix.uk": mat(g, H * d, r, 1.5), "m.mix.uv": mat(g, H * dv, r, 1.5), "m.mix.g": mat(g, H, hidden, 3.0), "m.mix.o": mat(g, hidden, H * dv, 1.5)}
+    return {k: bf(v) for k, v in w.items()}
+
+
+LATENTS = [_latent(3, 12, 6, 10, 20, 14, 0.3, 100.0, size=7), _latent(8, 32, 16, 32, 64, 48, 0.15, 1000.0, size=33),
+           _latent(16, 16, 16, 16, 112, 64, 0.18, 30000.0), _latent(2, 16, 8, 24, 32, 16, 0.2, 20.0, size=1),
+           _latent(4, 64, 16, 64, 64, 32, 0.11, 250.0, size=16)]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m", LATENTS, ids=lambda m: f"h{m['heads']}d{m['dim']}r{m['kv_rank']}w{(m.get('mask') or {}).get('size')}")
+def test_latent_attention_alone(dtype, m):
+    rt, hidden, T = runtime(dtype), 64, 90
+    w = latent_weights(hidden, m, 7)
+    x = bf(torch.randn(T, hidden, generator=torch.Generator().manual_seed(8)))
+    want = plain.latent_attention(x.double(), {k: v.double() for k, v in w.items()}, "m.mix", m, 1e-5)
+    part = build_mixer("latent_attention", m, hidden, 1e-5, rt, w)
+    for cuts in cuts_for(T):
+        runner = harness([part.cache_need()], rt, page=16)
+        close(feed([part], runner, x.to(rt.dtype), cuts)[0], want, dtype, f"cuts {cuts[:4]}")
+        runner.cache.check()
+
+
+def test_a_latent_window_gives_its_pages_back():
+    rt, hidden, T = runtime("float32"), 64, 120
+    m = LATENTS[0]
+    part = build_mixer("latent_attention", m, hidden, 1e-5, rt, latent_weights(hidden, m, 7))
+    runner = harness([part.cache_need()], rt, page=4, pages=6)          # far fewer pages than the sequence is long
+    x = bf(torch.randn(T, hidden, generator=torch.Generator().manual_seed(8)))
+    want = plain.latent_attention(x.double(), {k: v.double() for k, v in latent_weights(hidden, m, 7).items()}, "m.mix", m, 1e-5)
+    close(feed([part], runner, x.float(), portions(T, [3, 1, 2]))[0], want, "float32", "few pages")
+
+
+# ---- the state space layer ------------------------------------------------------------------------------------------------------
+
+def ssm_weights(hidden, m, seed, slow=False):
+    g = torch.Generator().manual_seed(seed)
+    H, P, N, G, taps = m["heads"], m["vdim"], m["state"], m["groups"], m["conv"]
+    inner, channels = H * P, H * P + 2 * G * N
+    w = {"m.mix.in": mat(g, 2 * inner + 2 * G * N + H, hidden, 1.5), "m.mix.conv": 0.6 * torch.randn(channels, taps, generator=g),
+         "m.mix.conv.b": 0.2 * torch.randn(channels, generator=g), "m.mix.dt_bias": -0.5 + 0.7 * torch.randn(H, generator=g),
+         "m.mix.A_log": (torch.full((H,), -6.0) if slow else torch.rand(H, generator=g) * 4.5 - 4.0), "m.mix.D": 1.0 + 0.3 * torch.randn(H, generator=g),
+         "m.mix.norm": 1.0 + 0.2 * torch.randn(inner, generator=g), "m.mix.o": mat(g, hidden, inner, 1.5)}
+    return {k: bf(v) for k, v in w.items()}
+
+
+SSMS = [_ssm(3, 10, 6, 1, 3, 1), _ssm(4, 32, 16, 2, 4, 2), _ssm(4, 16, 5, 4, 2, 4), _ssm(2, 24, 8, 1, 1, 1), _ssm(2, 40, 64, 2, 5, 1),
+        _ssm(1, 64, 130, 1, 4, 8)]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m", SSMS, ids=lambda m: f"h{m['heads']}p{m['vdim']}n{m['state']}g{m['groups']}c{m['conv']}")
+def test_state_space_layer_alone(dtype, m):
+    rt, hidden, T = runtime(dtype), 48, 120
+    w = ssm_weights(hidden, m, 11)
+    x = bf(torch.randn(T, hidden, generator=torch.Generator().manual_seed(12)))
+    want = plain.mamba2(x.double(), {k: v.double() for k, v in w.items()}, "m.mix", m, 1e-5)
+    part = build_mixer("mamba2", m, hidden, 1e-5, rt, w)
+    for cuts in cuts_for(T) + [[1] * T, portions(T, [17, 3, 1, 1, 2])]:
+        runner = harness([part.cache_need()], rt)
+        close(feed([part], runner, x.to(rt.dtype), cuts)[0], want, dtype, f"cuts {cuts[:4]}")
+    runner = harness([part.cache_need()], rt)                         # a slot that is used again starts from zeros
+    for req in ("a", "b", "c"):
+        close(feed([part], runner, x.to(rt.dtype), [50, 1, 1, T - 52], req=req)[0], want, dtype, req)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_slow_state_remembers_the_first_token(dtype):
+    """Decay rates so small that after 400 tokens the first one still weighs as much as the last: a state that is dropped or
+    zeroed between steps shows at once."""
+    rt, hidden, T = runtime(dtype), 32, 400
+    m = _ssm(2, 16, 8, 1, 2, 1)
+    w = ssm_weights(hidden, m, 13, slow=True)
+    x = 0.02 * torch.randn(T, hidden, generator=torch.Generator().manual_seed(14))
+    x[0] = 4.0 * torch.randn(hidden, generator=torch.Generator().manual_seed(15))
+    x = bf(x)
+    w64 = {k: v.double() for k, v in w.items()}
+    want = plain.mamba2(x.double(), w64, "m.mix", m, 1e-5)
+    without = plain.mamba2(x.double()[1:], w64, "m.mix", m, 1e-5)
+    assert (want[-1] - without[-1]).abs().max() > 0.05 * want[-1].abs().max()          # the first token does matter at the end
+    part = build_mixer("mamba2", m, hidden, 1e-5, rt, w)
+    for cuts in ([T], [T - 100] + [1] * 100, portions(T, [64, 1, 2])):
+        runner = harness([part.cache_need()], rt)
+        close(feed([part], runner, x.to(rt.dtype), cuts)[0], want, dtype, f"cuts {cuts[:3]}")
+
+
+# ---- feed-forwards ----------------------------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden,ff,T", [(40, 56, 9), (128, 256, 150), (64, 33, 1)])
+def test_dense_gelu_feed_forward_alone(dtype, hidden, ff, T):
+    from marin_b200.models.vogunex import _feedforward
+    from marin_b200.parts import lookup
+
+    rt = runtime(dtype)
+    g = torch.Generator().manual_seed(hidden)
+    w = {"f.up": bf(mat(g, ff, hidden, 2.0)), "f.up.b": bf(0.5 * torch.randn(ff, generator=g)), "f.down": bf(mat(g, hidden, ff, 1.5)),
+         "f.down.b": bf(0.3 * torch.randn(hidden, generator=g))}
+    x = bf(torch.randn(T, hidden, generator=g))
+    want = plain.dense_mlp(x.double(), {k: v.double() for k, v in w.items()}, "f")
+    spec = _feedforward({"kind": "dense", "ff": ff}, hidden)
+    part = lookup("feedforward", spec.kind)(name="f", **spec.params)
+    part.load(dict(w), rt)
+    runner = harness([], rt)
+    close(feed([part], runner, x.to(rt.dtype), [T], mixer=False)[0], want, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden,ff,E,top,shared,T", [(40, 24, 5, 2, 40, 23), (128, 64, 8, 2, 128, 300), (128, 128, 4, 1, 64, 7), (64, 64, 2, 2, None, 50),
+                                                        (64, 32, 3, 3, 32, 1), (128, 64, 16, 4, 64, 1200)])
+def test_capped_routed_experts_alone(dtype, hidden, ff, E, top, shared, T):
+    """Rows whose choice of experts is a close call in float64 (a router margin under 0.1) are left out: the rest must match in
+    both dtypes.  Limits of 0.8 and 1.5 with projections of order two: most values are capped on one side or the other."""
+    from marin_b200.config.vogunex import _mlp
+    from marin_b200.models.vogunex import _feedforward
+    from marin_b200.parts import lookup
+
+    rt = runtime(dtype)
+    g = torch.Generator().manual_seed(hidden + E)
+    mlp = _moe(ff, E, top, 0.8, shared=shared, shared_limit=1.5)
+    w = {"f.router": bf(mat(g, E, hidden, 4.0)), "f.router.b": bf(0.5 * torch.randn(E, generator=g))}
+    for e in range(E):
+        w[f"f.e{e}.gate"], w[f"f.e{e}.up"], w[f"f.e{e}.down"] = bf(mat(g, ff, hidden, 2.0)), bf(mat(g, ff, hidden, 2.0)), bf(mat(g, hidden, ff, 1.5))
+    if shared:
+        w["f.shared.gate"], w["f.shared.up"] = bf(mat(g, shared, hidden, 2.0)), bf(mat(g, shared, hidden, 2.0))
+        w["f.shared.down"], w["f.shared.sg"] = bf(mat(g, hidden, shared, 1.5)), bf(mat(g, 1, hidden, 3.0))
+    w64 = {k: v.double() for k, v in w.items()}
+    x = bf(torch.randn(2 * T + 8, hidden, generator=g))
+    x = x[plain.router_margins(x.double(), w64, "f", mlp) > 0.1][:T].contiguous()
+    want = plain.routed_mlp(x.double(), w64, "f", mlp)
+    spec = _feedforward(_mlp(mlp, ""), hidden)
+    part = lookup("feedforward", spec.kind)(name="f", **spec.params)
+    part.load(dict(w), rt)
+    runner = harness([], rt)
+    close(feed([part], runner, x.to(rt.dtype), [x.shape[0]], mixer=False)[0], want, dtype)
+
+
+# ---- whole models -----------------------------------------------------------------------------------------------------------------
+
+class Case:
+    def __init__(self, tmp, name, dtype):
+        from marin_b200.engine import load_model
+
+        self.name, self.dtype = name, dtype
+        self.raw = CONFIGS[name]
+        self.dir = make_model_dir(str(tmp / f"{name}-{dtype}"), name, seed=11)
+        self.w = plain.read_weights(self.dir)
+        rng = random.Random(5)
+        self.tokens = {rid: random_prompt(rng, self.raw["vocab"], n) for rid, n in LENGTHS[name].items()}
+        self.want, self.safe = {}, {}
+        for rid, t in self.tokens.items():
+            margins = []
+            self.want[rid] = plain.forward(self.raw, self.w, t, None, margins)
+            tight = torch.stack(margins).min(dim=0).values < 0.1 if margins else torch.zeros(len(t), dtype=torch.bool)
+            self.safe[rid] = int(torch.nonzero(tight)[0]) if bool(tight.any()) else len(t)
+        self.rt = runtime(dtype)
+        self.config, self.model = load_model(self.dir, self.rt)
+        self.page = PAGE[name]
+        self.loose = 0.0 if dtype == "float32" else 0.02
+
+    def runner(self, num_pages, max_requests=4, graphs=False):
+        from marin_b200.cache import CacheManager
+        from marin_b200.engine import Runner
+
+        cache = CacheManager(self.model.cache_needs(), [e.cache_of for e in self.model.spec.schedule], self.page, num_pages, max_requests)
+        cache.allocate(self.rt.device, self.rt.dtype)
+        runner = Runner(self.model, cache, self.rt, 512)
+        if graphs:
+            runner.enable_graphs((1, 2, 4))
+        return runner
+
+    def close(self, got, rid, what):
+        close(got, self.want[rid], self.dtype, what, self.loose, self.safe[rid])
+
+
+@pytest.fixture(scope="module", params=[(n, d) for n in CONFIGS for d in DTYPES], ids=lambda p: f"{p[0]}-{p[1]}")
+def case(request, tmp_path_factory):
+    return Case(tmp_path_factory.mktemp("vogunex"), *request.param)
+
+
+def test_the_residual_stream_after_every_layer(case):
+    from marin_b200.engine import StepEntry
+
+    rid = "a"
+    want = []
+    plain.forward(case.raw, case.w, case.tokens[rid], want)
+    got = {}
+    runner = case.runner(64)
+    runner.begin(rid)
+    runner.step([StepEntry(rid, case.tokens[rid], [0])], observe=lambda i, h: got.__setitem__(i, h.clone()))
+    assert len(got) == len(want) + 1
+    for i in range(len(want)):
+        close(got[i + 1], want[i], case.dtype, f"after layer {i}", case.loose, case.safe[rid])
+
+
+def test_whole_prompts_and_the_first_tokens(case):
+    runner = case.runner(64)
+    for rid, tokens in case.tokens.items():
+        case.close(run_whole(runner, rid, tokens), rid, f"{rid} whole")
+    runner.cache.check()
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_prefill_then_token_by_token(case, graphs):
+    """Most of a prompt in one step and the rest one token at a time, eagerly and from captured graphs: a tail long enough for
+    every window to pass wholly over decoded tokens and for blocks to become whole among them; and a request decoded from
+    its very first token."""
+    runner = case.runner(64, graphs=graphs)
+    for rid, tail in (("c", 100), ("a", 30), ("e", 5)):
+        tokens = case.tokens[rid]
+        n = max(len(tokens) - tail, 0)
+        sizes = ([n] if n > 0 else []) + [1] * (len(tokens) - n)
+        case.close(run_portions(runner, rid + "t", tokens, sizes), rid, f"{rid}, last {tail} one by one")
+    rid = "e"
+    case.close(run_portions(runner, rid + "1", case.tokens[rid], [1] * len(case.tokens[rid])), rid, f"{rid} token by token")
+    runner.cache.check()
+
+
+def test_portions_of_changing_size_down_to_two_tokens(case):
+    runner = case.runner(64)
+    for rid in ("c", "a"):
+        tokens = case.tokens[rid]
+        for sizes in ([7, 2, 13, 3, 2, 5], [2], [case.page, case.page + 1, case.page - 1], [64, 1, 2]):
+            case.close(run_portions(runner, rid + "p", tokens, portions(len(tokens), sizes)), rid, f"{rid} in {sizes}")
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_mixed_batches_reuse_pages_and_slots(case, graphs):
+    """Up to four live requests, portions of some beside single tokens of others, in a pool that holds the four largest only:
+    pages (with their pooled rows) and slots of finished requests are handed to the next ones."""
+    rng = random.Random(9)
+    lengths = {rid: len(t) for rid, t in case.tokens.items()}
+    sched = mixed_schedule(rng, lengths, max_live=4, decode_tail=6)
+    pool = sum(sorted((-(-n // case.page) for n in lengths.values()), reverse=True)[:4])
+    runner = case.runner(pool, max_requests=4, graphs=graphs)
+    got = run_mixed(runner, case.tokens, sched)
+    for rid in case.tokens:
+        case.close(got[rid], rid, f"{rid} mixed")
+    runner.cache.check()
+    assert all(g.pool.num_held == 0 for g in runner.cache.groups)
+    again = run_mixed(runner, case.tokens, sched)
+    for rid in case.tokens:
+        case.close(again[rid], rid, f"{rid} mixed, second time")
+
+
+def test_a_batch_gives_each_request_what_it_gets_alone(case):
+    """float32: the logits of a request are the same bits whatever else the step holds and however its prompt was cut."""
+    if case.dtype != "float32":
+        pytest.skip("bit equality is the 32-bit path's claim")
+    from marin_b200.engine import StepEntry
+
+    runner = case.runner(64)
+    alone = {rid: run_whole(runner, rid, case.tokens[rid]) for rid in ("a", "b", "e")}
+    for rid in alone:
+        runner.begin(rid)
+    logits = runner.step([StepEntry(rid, case.tokens[rid], list(range(len(case.tokens[rid])))) for rid in ("a", "b", "e")])
+    k = 0
+    for rid in ("a", "b", "e"):
+        n = len(case.tokens[rid])
+        assert torch.equal(logits[k:k + n], alone[rid]), rid
+        k += n
+        runner.end(rid)
+    cut = run_portions(runner, "ap", case.tokens["a"], portions(len(case.tokens["a"]), [5, 2, 9, 1]))
+    assert torch.equal(cut, alone["a"])
+
+
+def test_greedy_generation_through_the_engine(case):
+    """The entry point, the scheduler and device sampling: the tokens are those the plain implementation's logits rank first (a
+    token whose plain logit lies within 1e-3 (32-bit) or 0.15 (16-bit) of the largest counts as first; in 16 bits a sequence
+    is followed only as far as no choice of experts is a close call)."""
+    from marin_b200.engine import Engine
+    from marin_b200.sampling.sampler import SamplingParams
+
+    engine = Engine(case.dir, dtype=case.dtype, ctx=256, page_size=case.page, num_pages=64, max_batch=4, token_budget=32)
+    prompts = [case.tokens["a"][:21], case.tokens["e"][:3], case.tokens["c"][:40]]
+    outs = engine.generate(prompts, SamplingParams(temperature=0.0, max_tokens=10))
+    slack = 1e-3 if case.dtype == "float32" else 0.15
+    for prompt, out in zip(prompts, outs):
+        assert len(out.tokens) == 10
+        seq = list(prompt)
+        for token in out.tokens:
+            margins = []
+            logits = plain.forward(case.raw, case.w, seq, None, margins)[-1]
+            if case.dtype != "float32" and margins and min(float(mm.min()) for mm in margins) < 0.1:
+                break
+            assert logits[token] >= logits.max() - slack, (len(seq), token, int(logits.argmax()))
+            seq.append(token)
+
+
+def test_trace_replay_as_a_user_runs_it(tmp_path):
+    """bin/trace_run in a process of its own: steps on standard input, logits read back from files."""
+    name, dtype = "B", "float32"
+    raw = CONFIGS[name]
+    d = make_model_dir(str(tmp_path / "model"), name, seed=12)
+    w = plain.read_weights(d)
+    rng = random.Random(3)
+    lengths = {"a": 70, "b": 130, "c": 41, "d": 64, "e": 100, "f": 2}
+    tokens = {rid: random_prompt(rng, raw["vocab"], n) for rid, n in lengths.items()}
+    want = {rid: plain.forward(raw, w, t) for rid, t in tokens.items()}
+    sched = mixed_schedule(rng, lengths, max_live=4, decode_tail=5)
+    pool = sum(sorted((-(-n // 64) * 64 for n in lengths.values()), reverse=True)[:4])
+    out = str(tmp_path / "out")
+    proc = subprocess.Popen([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", d, "--dtype", dtype, "--out", out,
+                             "--max-tokens", str(pool)], stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True)
+    fed = {rid: 0 for rid in tokens}
+    for i, (entries, ends) in enumerate(sched):
+        line, rows = [], []
+        for rid, n in entries:
+            wanted = [n - 1] if n > 2 else list(range(n))
+            line.append({"id": rid, "tokens": tokens[rid][fed[rid]:fed[rid] + n], "want": wanted})
+            rows.append(want[rid][[fed[rid] + k for k in wanted]])
+            fed[rid] += n
+        proc.stdin.write(json.dumps({"step": i, "entries": line, "end": ends}) + "\n")
+        proc.stdin.flush()
+        assert proc.stdout.readline().strip() == f"done {i}"
+        got = torch.from_numpy(np.fromfile(os.path.join(out, f"{i}.f32"), dtype="<f4").reshape(-1, raw["vocab"]).copy())
+        close(got, torch.cat(rows), dtype, f"step {i}")
+    proc.stdin.close()
+    assert proc.wait(timeout=120) == 0
+
+
+def test_the_command_line_takes_a_vogunex_folder(tmp_path):
+    """Random-weights mode from a config.json of this design, greedy generation, and the bench command with its stage table."""
+    run = [sys.executable, os.path.join(ROOT, "bin", "marin-run")]
+    cfg = tmp_path / "cfg.json"
+    cfg.write_text(json.dumps(CONFIGS["B"]))
+    model = str(tmp_path / "model")
+    out = subprocess.run(run + ["random", "--config", str(cfg), "--seed", "3", "--out", model], capture_output=True, text=True)
+    assert out.returncode == 0, out.stderr
+    assert sorted(os.listdir(model)) == ["config.json", "model.safetensors"]
+    a = subprocess.run(run + [model, "--prompt-ids", "5,6,7,8,9", "--temp", "0", "--max-tokens", "6"], capture_output=True, text=True)
+    b = subprocess.run(run + [model, "--prompt-ids", "5 6 7 8 9", "--temp", "0", "--max-tokens", "6"], capture_output=True, text=True)
+    assert a.returncode == 0 and b.returncode == 0, a.stderr + b.stderr
+    assert a.stdout == b.stdout and len(a.stdout.split()) == 6
+    e = subprocess.run(run + ["bench", model, "--prompt-tokens", "16", "--tokens", "8", "--runs", "2", "--warmup", "1", "--profile"],
+                       capture_output=True, text=True)
+    assert e.returncode == 0, e.stderr
+    for stage in ("embedding", "token shift", "q|k|v", "pooled blocks", "attention", "q|dkv", "q from its latent", "convolution", "recurrence",
+                  "gate, norm", "router", "experts", "up, activation", "head", "sampling"):
+        assert stage in e.stdout, stage
