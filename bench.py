@@ -2,7 +2,7 @@
 """Decode and prefill throughput of the engine on one B200, with their fractions of roofline.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers N] [--impl ours|reference]
-    python bench.py --arch lakulix|fegarax|nirotar [--model 4b|8b|14b] [--layers 12] [--batch 8] [--profile]
+    python bench.py --arch lakulix|fegarax|nirotar|vogunex [--model 4b|8b|14b] [--layers 12] [--batch 8] [--profile]
 
 The default run has the layer sizes of the Qwen3-4B layout with random bfloat16 weights, a batch of 8
 sequences and a context of 4096 positions (the last timed step reaches it).  A "step" is one decode
@@ -24,6 +24,9 @@ attention with the layout's heads, a gate and a sink, eight experts of half the 
 ``--arch nirotar`` measures Nirotar layers (windowed attention with a learned sink and attention over a shared latent in turn,
 experts without a gate chosen by a table over the token ids, a shared expert) beside the Fegarax layout of the same width,
 depth, vocabulary and heads, the closest of the engine's models (attention with a sink, routed experts).
+``--arch vogunex`` measures Vogunex layers (attention over a window and pooled blocks with mixed head weights, a state space
+layer, attention over a shared latent with a window, in turn; dense and routed feed-forwards; a token shift before every
+mixer) beside the Nirotar layers at the same sizes, the closest of the engine's models.
 The default workload and its line are not touched by any of them.
 
 Peaks come from MEASURED_PEAKS.json beside this file if present, else 6.65 TB/s and 1.59 PFLOP/s.
@@ -142,7 +145,7 @@ def fill_cache(engine, seed=1):
 
     g = torch.Generator(device=engine.rt.device).manual_seed(seed)
     for group in engine.cache.groups:
-        for t in (group.k, group.v):
+        for t in (group.k, group.v) + ((group.k_pool, group.v_pool) if group.k_pool is not None else ()):
             flat = t.view(-1)
             step = 1 << 28
             for at in range(0, flat.numel(), step):
@@ -368,6 +371,34 @@ def nirotar_layout(raw: dict, layers: int) -> dict:
             "max_positions": 2 * CONTEXT, "layers": out}
 
 
+VOGUNEX_LAYERS = ("in turn: attention with the layout's heads (a window of 1,024 positions and, before it, one pooled key and value per "
+                  "block of 64; half of every head rotated, scores capped, the heads' weights mixed) with a dense gelu feed-forward; a "
+                  "selective state space layer (heads of 64 filling the width, a state of 128 rows, one group, four taps) with experts; "
+                  "attention again; attention over a shared latent (as many heads, 64 unrotated + 32 rotated query numbers through a "
+                  "latent of 768, values of 64, page rows of 128 + 32 numbers, a window of 1,024, a gate per head) with experts.  A token "
+                  "shift in front of every mixer.  8 gated experts with capped inputs of 3/8 of the layout's feed-forward width, 2 chosen, "
+                  "and a shared expert of a quarter of it: as many active feed-forward weights per token as the dense layouts")
+
+
+def vogunex_layout(raw: dict, layers: int) -> dict:
+    """A Vogunex configuration at a Qwen3 layout's sizes: the same width, vocabulary and attention heads; feed-forwards that
+    activate as many weights per token as the layout's dense gated one (a dense one without a gate is half as wide again)."""
+    head, heads, width, ff = raw["head_dim"], raw["num_attention_heads"], raw["hidden_size"], raw["intermediate_size"]
+    attention = {"heads": heads, "kv_heads": raw["num_key_value_heads"], "dim": head, "vdim": head, "scale": head ** -0.5, "softcap": 50.0,
+                 "mask": {"size": 1024, "pool": 64}, "rot": {"base": 500000.0, "dims": head // 2}}
+    latent = {"heads": heads, "dim": 64, "rot_dim": 32, "vdim": 64, "kv_rank": 128, "q_rank": 768, "scale": 96 ** -0.5, "mask": {"size": 1024},
+              "rot": {"base": 500000.0, "dims": 32}}
+    ssm = {"heads": width // 64, "vdim": 64, "state": 128, "groups": 1, "conv": 4, "norm_groups": 1}
+    expert = ff * 3 // 8 // 64 * 64
+    moe = {"kind": "moe", "expert": {"ff": expert, "limit": 7.0}, "router": {"experts": 8, "top": 2},
+           "shared": {"ff": (ff - 2 * expert) // 64 * 64, "limit": 7.0}}
+    dense = {"kind": "dense", "ff": ff * 3 // 2 // 64 * 64}
+    kinds = [("attention", attention, dense), ("mamba2", ssm, moe), ("attention", attention, dense), ("latent_attention", latent, moe)]
+    return {"architecture": "Vogunex", "vocab": raw["vocab_size"], "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+            "max_positions": 2 * CONTEXT,
+            "layers": [{"type": kinds[i % 4][0], "mixer": kinds[i % 4][1], "mlp": kinds[i % 4][2]} for i in range(layers)]}
+
+
 def arch_mode(args, pk, arch: str) -> int:
     """Decode and prompt throughput of another architecture at a Qwen3 layout's sizes, and of that Qwen3 layout at the same
     depth, with their fractions of roofline: one JSON line.  With --profile: the architecture's stage tables."""
@@ -376,21 +407,25 @@ def arch_mode(args, pk, arch: str) -> int:
     import torch
 
     from marin_b200 import Engine
-    from marin_b200.config import FegaraxConfig, LakulixConfig, NirotarConfig, Qwen3Config
+    from marin_b200.config import FegaraxConfig, LakulixConfig, NirotarConfig, Qwen3Config, VogunexConfig
 
     layers = args.layers or 12
     raw = dict(LAYOUTS[args.model], num_hidden_layers=layers)
     warmup = max(3, args.warmup)
     title = arch.capitalize()
     # the model it is measured beside: the Qwen3 layout, or for Nirotar the engine's closest model, Fegarax at that layout's sizes
-    beside = "fegarax" if arch == "nirotar" else "qwen3"
-    if arch == "lakulix":
+    # (for Vogunex: Nirotar, whose windowed and latent attention and experts with a shared one are the nearest kernels)
+    beside = "fegarax" if arch == "nirotar" else "nirotar" if arch == "vogunex" else "qwen3"
+    if arch == "vogunex":
+        other = VogunexConfig.from_dict(vogunex_layout(raw, layers))
+    elif arch == "lakulix":
         other = LakulixConfig.from_dict(lakulix_layout(raw, layers))
     elif arch == "fegarax":
         other = FegaraxConfig.from_dict(fegarax_layout(raw, layers))
     else:
         other = NirotarConfig.from_dict(nirotar_layout(raw, layers))
-    arms = {arch: other, beside: FegaraxConfig.from_dict(fegarax_layout(raw, layers)) if beside == "fegarax" else Qwen3Config.from_dict(raw)}
+    arms = {arch: other, beside: FegaraxConfig.from_dict(fegarax_layout(raw, layers)) if beside == "fegarax" else
+            NirotarConfig.from_dict(nirotar_layout(raw, layers)) if beside == "nirotar" else Qwen3Config.from_dict(raw)}
     out = {}
     for name, cfg in arms.items():
         if args.profile and name != arch:
@@ -410,7 +445,9 @@ def arch_mode(args, pk, arch: str) -> int:
         # a layer that keeps a state reads the same bytes whatever the context; a layer that keeps keys reads them all
         state_bytes = sum(n.bytes() for n in engine.cache.state_needs.values())
         # (a layer with a window reads the window's positions, however long the sequence)
-        paged = sum(len(g.entries) * g.need.bytes_per_token(engine.rt.dtype) * min(run["mean_context"], g.need.window or run["mean_context"])
+        # (one with pooled blocks: the window's positions and one row per block before it)
+        paged = sum(len(g.entries) * (g.need.bytes_read(int(run["mean_context"]), engine.rt.dtype) if g.need.pooled else
+                                      g.need.bytes_per_token(engine.rt.dtype) * min(run["mean_context"], g.need.window or run["mean_context"]))
                     for g in engine.cache.groups)
         step_bytes = weight_bytes + args.batch * (paged + 2 * state_bytes)
         achieved = step_bytes / (run["ms_per_step"] / 1e3) / 1e9
@@ -425,13 +462,13 @@ def arch_mode(args, pk, arch: str) -> int:
         gc.collect()
         torch.cuda.empty_cache()
     print(json.dumps({
-        "metric": f"{title} beside the {'Fegarax layers at the ' if beside == 'fegarax' else ''}Qwen3-{args.model.upper()} layout at equal width, depth and vocabulary: decode tok/s at batch {args.batch} "
+        "metric": f"{title} beside the {'Fegarax layers at the ' if beside == 'fegarax' else 'Nirotar layers at the ' if beside == 'nirotar' else ''}Qwen3-{args.model.upper()} layout at equal width, depth and vocabulary: decode tok/s at batch {args.batch} "
                   f"(context {CONTEXT}), prefill tok/s at {PREFILL_TOKENS} tokens, fractions of roofline",
         "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup, "dtype": "bf16", "higher_is_better": True,
         "data": "synthetic (uniform random token ids, seeded random weights)", "peaks": pk,
         "config": {"layers": layers, "width": raw["hidden_size"], "ff": raw["intermediate_size"], "vocab": raw["vocab_size"],
                    "global_batch": args.batch, "seq_len": CONTEXT, "prefill_tokens": PREFILL_TOKENS, "kv_block": PAGE,
-                   f"{arch}_layers": FEGARAX_LAYERS if arch == "fegarax" else NIROTAR_LAYERS if arch == "nirotar" else
+                   f"{arch}_layers": FEGARAX_LAYERS if arch == "fegarax" else NIROTAR_LAYERS if arch == "nirotar" else VOGUNEX_LAYERS if arch == "vogunex" else
                    "lightning (heads of 128 x 128), attention (the layout's heads), wkv (heads of 64) in turn, a dense feed-forward in each",
                    "l2": "inputs larger than L2 (weights read per step exceed 126 MB)"},
         arch: out[arch], beside: out[beside], "impl": "ours"}))
@@ -459,9 +496,9 @@ def main() -> int:
     ap.add_argument("--model", default="4b", choices=sorted(LAYOUTS), help="layer sizes: Qwen3-4B (the default), 8B or 14B layout")
     ap.add_argument("--context", type=int, default=CONTEXT, help="context length the last timed decode step reaches (default 4096)")
     ap.add_argument("--profile", action="store_true", help="print where a step's time goes, stage by stage, instead of the JSON line")
-    ap.add_argument("--arch", default="qwen3", choices=["qwen3", "lakulix", "fegarax", "nirotar"],
+    ap.add_argument("--arch", default="qwen3", choices=["qwen3", "lakulix", "fegarax", "nirotar", "vogunex"],
                     help="qwen3: the default workload; lakulix, fegarax: that architecture at the layout's sizes beside the Qwen3 layout of "
-                         "equal size; nirotar: beside the Fegarax layers at that layout's sizes")
+                         "equal size; nirotar: beside the Fegarax layers at that layout's sizes; vogunex: beside the Nirotar layers at those sizes")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()

@@ -212,12 +212,13 @@ def attention_tc_name(d: int, group: int, dv: int = 0, values_in_keys: bool = Fa
 
 #: One or two layouts of every source that is otherwise compiled for a model's own sizes when it first runs (the names and
 #: defines are those the wrappers in ``ops`` use): sink attention with keys and values of their own and over a shared latent
-#: with sixteen heads a CTA, sigmoid attention, chunked linear attention.
+#: with sixteen heads a CTA, sigmoid attention, chunked linear attention, attention over a window and pooled blocks.
 PER_LAYOUT_SAMPLES = {
     "mb_attention_sink_fast_d128_v128_g4": (["attention_sink_fast.cu"], ["HEAD_DIM=128", "V_DIM=128", "GROUP=4"]),
     "mb_attention_sink_fast_d160_v128_g16_vk": (["attention_sink_fast.cu"], ["HEAD_DIM=160", "V_DIM=128", "GROUP=16", "V_IN_K"]),
     "mb_attention_sigmoid_fast_d128_v128_g4": (["attention_sigmoid_fast.cu"], ["HEAD_DIM=128", "V_DIM=128", "GROUP=4"]),
     "mb_linear_attention_chunked_d128_v32": (["linear_attention_chunked.cu"], ["QK_DIM=128", "V_SLICE=32"]),
+    "mb_attention_pooled_fast_d128_v128_g4_c2": (["attention_pooled_fast.cu"], ["HEAD_DIM=128", "V_DIM=128", "GROUP=4", "VALUE_HEADS=2"]),
 }
 
 

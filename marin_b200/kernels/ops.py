@@ -1704,19 +1704,73 @@ def attention_pooled(q, k_cache, v_cache, k_pool, v_pool, out, ctx, block_table,
         return
     size = q.element_size()
     parts = ctx.workspace.get("pooled_parts", (T, H, K, dv), torch.float32) if talk is not None else None
-    if launch_log is not None:
-        _cost(T * H * (d + dv) * size, 0.0, K * (d + dv) * size, 2.0 * H * (d + (K if talk is not None else 1) * dv))
-        _pending_cost["rows"], _pending_cost["window"] = "all", window
     rows = -(-page_size // pool) if pool else 0
-    _check(_lib("mb_attention_pooled").mb_attention_pooled(
-        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(k_pool), _ptr(v_pool), _ptr(parts), _ptr(out), _code(q), _ptr(block_table),
-        _c_int(block_table.shape[1]), _ptr(ctx.req_index), _ptr(ctx.positions), _ptr(ctx.seq_lens), _c_int(T), _c_int(H), _c_int(K), _c_int(d),
-        _c_int(dv), _c_int(page_size), _c_float(scale), _c_float(softcap or 0.0), _c_int(window), _c_int(pool), _c_int(rows),
-        _c_int(int(talk is not None)), _stream()), "attention (window and pooled blocks)")
+    pair_flops = 2.0 * H * (d + (K if talk is not None else 1) * dv)
+    plain_tokens = T
+    if use_fast_pooled_attention and fast_pooled_attention_supported(q.dtype, H, K, d, dv) and page_size & (page_size - 1) == 0:
+        # prompt portions on the tensor cores; the single tokens (the step's first rows) stay with the plain kernel
+        plain_tokens = nd = ctx.num_decode
+        if ctx.num_requests > nd:
+            if launch_log is not None:
+                _cost((T - nd) * H * (d + dv) * size, 0.0, K * (d + dv) * size, pair_flops)
+                _pending_cost["rows"], _pending_cost["window"] = "prefill", window
+            lib = _pooled_lib(d, dv, H // K, pooled_value_heads(K, dv))
+            _check(lib.mb_attn_pooled_prefill(
+                _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(k_pool), _ptr(v_pool), _ptr(parts), _ptr(out), _ptr(block_table),
+                _c_int(block_table.shape[1]), _ptr(ctx.cu_tokens), _ptr(ctx.seq_lens), _c_int(nd), _c_int(ctx.num_requests - nd),
+                _c_int(ctx.max_query_len), _c_int(K), _c_int(page_size), _c_float(scale), _c_float(softcap or 0.0), _c_int(window), _c_int(pool),
+                _c_int(rows), _c_int(int(talk is not None)), _stream()), "attention (window and pooled blocks, prefill, tensor cores)")
+    if plain_tokens > 0:
+        if launch_log is not None:
+            _cost(plain_tokens * H * (d + dv) * size, 0.0, K * (d + dv) * size, pair_flops)
+            _pending_cost["rows"], _pending_cost["window"] = ("all" if plain_tokens == T else "decode"), window
+        _check(_lib("mb_attention_pooled").mb_attention_pooled(
+            _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(k_pool), _ptr(v_pool), _ptr(parts), _ptr(out), _code(q), _ptr(block_table),
+            _c_int(block_table.shape[1]), _ptr(ctx.req_index), _ptr(ctx.positions), _ptr(ctx.seq_lens), _c_int(plain_tokens), _c_int(H), _c_int(K),
+            _c_int(d), _c_int(dv), _c_int(page_size), _c_float(scale), _c_float(softcap or 0.0), _c_int(window), _c_int(pool), _c_int(rows),
+            _c_int(int(talk is not None)), _stream()), "attention (window and pooled blocks)")
     if talk is not None:
         _cost(_size(parts) + _size(out), 2.0 * T * H * H * dv)
         _check(_lib("mb_attention_pooled").mb_talk_mix(_ptr(parts), _ptr(talk), _ptr(out), _code(out), _c_int(T), _c_int(H), _c_int(K), _c_int(dv),
                                                       _stream()), "heads' weights mixed")
+
+
+#: bf16 prompt portions of attention over a window and pooled blocks go to the tensor-core kernel where the head layout allows
+use_fast_pooled_attention = True
+
+
+def fast_pooled_attention_supported(dtype, H: int, K: int, d: int, dv: int) -> bool:
+    """Head sizes in multiples of 16 up to 128."""
+    return dtype == torch.bfloat16 and d % 16 == 0 and dv % 16 == 0 and 16 <= d <= 128 and 16 <= dv <= 128 and H % K == 0
+
+
+def pooled_value_heads(K: int, dv: int) -> int:
+    """Kv heads whose values a CTA of the tensor-core kernel sums at a time: as many as its registers hold (256 columns),
+    a divisor of ``K``."""
+    most = max(1, 256 // dv)
+    return max(v for v in range(1, min(K, most) + 1) if K % v == 0)
+
+
+def _pooled_job(d: int, dv: int, group: int, value_heads: int) -> tuple:
+    return (["attention_pooled_fast.cu"], [f"HEAD_DIM={d}", f"V_DIM={dv}", f"GROUP={group}", f"VALUE_HEADS={value_heads}"])
+
+
+def _pooled_name(d: int, dv: int, group: int, value_heads: int) -> str:
+    return f"mb_attention_pooled_fast_d{d}_v{dv}_g{group}_c{value_heads}"
+
+
+def _pooled_lib(d: int, dv: int, group: int, value_heads: int):
+    return build.load(_pooled_name(d, dv, group, value_heads), *_pooled_job(d, dv, group, value_heads))
+
+
+def pooled_attention_jobs(dtype, H: int, K: int, d: int, dv: int) -> dict:
+    """The kernels a mixer with this head layout runs: head preparation, the plain kernels, and the tensor-core kernel compiled
+    for the layout where it allows."""
+    jobs = library_jobs("mb_attention_sink", "mb_attention_pooled")
+    if use_fast_pooled_attention and fast_pooled_attention_supported(dtype, H, K, d, dv):
+        vh = pooled_value_heads(K, dv)
+        jobs[_pooled_name(d, dv, H // K, vh)] = _pooled_job(d, dv, H // K, vh)
+    return jobs
 
 
 # ---- a selective state space layer (csrc/ssm.cu) ---------------------------------------------------------------------------------

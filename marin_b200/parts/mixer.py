@@ -719,7 +719,7 @@ class PooledAttention(Mixer):
         return super().flops(tokens, pairs) + 2.0 * pairs * self.heads * (self.head_dim + values)
 
     def kernel_jobs(self, dtype) -> Dict[str, tuple]:
-        return ops.library_jobs("mb_attention_sink", "mb_attention_pooled")
+        return ops.pooled_attention_jobs(dtype, self.heads, self.kv_heads, self.head_dim, self.v_head_dim)
 
     def forward(self, x, ctx, cache, residual: torch.Tensor):
         T = x.shape[0]
