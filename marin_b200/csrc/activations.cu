@@ -232,26 +232,28 @@ MB_API int mb_relu2(void* x, int dtype, size_t total, cudaStream_t s) {
 __device__ __forceinline__ float gelu_erf_f(float v) { return 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f)); }
 __device__ __forceinline__ float gelu_tanh_f(float v) { return 0.5f * v * (1.0f + tanhf(0.79788456080286535588f * (v + 0.044715f * v * v * v))); }
 
+// (a row per blockIdx.x, its columns over blockIdx.y and the threads: no division per element)
 template <typename T>
-__global__ void bias_act_kernel(T* __restrict__ x, const float* __restrict__ b, size_t total, int n, int act) {
+__global__ void bias_act_kernel(T* __restrict__ x, const float* __restrict__ b, int n, int act) {
     PDL_ENTER();
     x = pdl_fresh(x);
-    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const size_t stride = (size_t)gridDim.x * blockDim.x;
-    for (; idx < total; idx += stride) {
-        float v = to_f32(x[idx]) + (b != nullptr ? b[idx % (size_t)n] : 0.0f);
+    T* row = x + (size_t)blockIdx.x * n;
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < n; i += gridDim.y * blockDim.x) {
+        float v = to_f32(row[i]) + (b != nullptr ? b[i] : 0.0f);
         if (act == 1) v = gelu_erf_f(v);
         else if (act == 2) v = gelu_tanh_f(v);
-        x[idx] = from_f32<T>(v);
+        row[i] = from_f32<T>(v);
     }
 }
+
+static inline dim3 row_grid(int rows, int n) { return dim3(rows, (n + 1023) / 1024 < 64 ? (n + 1023) / 1024 : 64); }
 
 MB_API int mb_bias_act(void* x, int dtype, const float* b, int rows, int n, int act, cudaStream_t s) {
     const size_t total = (size_t)rows * n;
     if (total == 0) return 0;
     if (act < 0 || act > 2) return MB_ERR_BAD_SIZE;
-    if (dtype == MB_F32) return launch_kernel(bias_act_kernel<float>, blocks_for(total, 256), 256, 0, s, 0, (float*)x, b, total, n, act);
-    if (dtype == MB_BF16) return launch_kernel(bias_act_kernel<bf16>, blocks_for(total, 256), 256, 0, s, 0, (bf16*)x, b, total, n, act);
+    if (dtype == MB_F32) return launch_kernel(bias_act_kernel<float>, row_grid(rows, n), 256, 0, s, 0, (float*)x, b, n, act);
+    if (dtype == MB_BF16) return launch_kernel(bias_act_kernel<bf16>, row_grid(rows, n), 256, 0, s, 0, (bf16*)x, b, n, act);
     return MB_ERR_BAD_DTYPE;
 }
 
@@ -263,18 +265,13 @@ __global__ void glu_capped_kernel(const T* __restrict__ rows, int stride, T* __r
                                   float shift, int scale_col) {
     PDL_ENTER();
     rows = pdl_fresh(rows);
-    const size_t total = (size_t)tokens * ff;
-    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const size_t step = (size_t)gridDim.x * blockDim.x;
-    for (; idx < total; idx += step) {
-        const size_t t = idx / (size_t)ff;
-        const int c = (int)(idx - t * ff);
-        const T* row = rows + t * stride;
+    const size_t t = blockIdx.x;
+    const T* row = rows + t * stride;
+    const float row_scale = scale_col >= 0 ? 1.0f / (1.0f + expf(-to_f32(row[scale_col]))) : 1.0f;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < ff; c += gridDim.y * blockDim.x) {
         float g = to_f32(row[c]), u = to_f32(row[ff + c]);
         if (limit > 0.0f) { g = fminf(g, limit); u = fminf(fmaxf(u, -limit), limit); }
-        float v = g / (1.0f + expf(-alpha * g)) * (u + shift);
-        if (scale_col >= 0) v *= 1.0f / (1.0f + expf(-to_f32(row[scale_col])));
-        out[idx] = from_f32<T>(v);
+        out[t * ff + c] = from_f32<T>(g / (1.0f + expf(-alpha * g)) * (u + shift) * row_scale);
     }
 }
 
@@ -284,10 +281,10 @@ MB_API int mb_glu_capped(const void* rows, int stride, int dtype, void* out, int
     if (total == 0) return 0;
     if (stride < 2 * ff || scale_col >= stride) return MB_ERR_BAD_SIZE;
     if (dtype == MB_F32)
-        return launch_kernel(glu_capped_kernel<float>, blocks_for(total, 256), 256, 0, s, 0, (const float*)rows, stride, (float*)out, tokens, ff,
+        return launch_kernel(glu_capped_kernel<float>, row_grid(tokens, ff), 256, 0, s, 0, (const float*)rows, stride, (float*)out, tokens, ff,
                              limit, alpha, shift, scale_col);
     if (dtype == MB_BF16)
-        return launch_kernel(glu_capped_kernel<bf16>, blocks_for(total, 256), 256, 0, s, 0, (const bf16*)rows, stride, (bf16*)out, tokens, ff,
+        return launch_kernel(glu_capped_kernel<bf16>, row_grid(tokens, ff), 256, 0, s, 0, (const bf16*)rows, stride, (bf16*)out, tokens, ff,
                              limit, alpha, shift, scale_col);
     return MB_ERR_BAD_DTYPE;
 }
@@ -341,18 +338,17 @@ MB_API int mb_keep_last_row(const void* h, int dtype, float* carry, long long st
 }
 
 // ---- a bias added to every row of the float32 residual: y[t, i] += b[i] -----------------------------------------------------
-__global__ void add_row_bias_kernel(float* __restrict__ y, const float* __restrict__ b, size_t total, int n) {
+__global__ void add_row_bias_kernel(float* __restrict__ y, const float* __restrict__ b, int n) {
     PDL_ENTER();
     y = pdl_fresh(y);
-    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const size_t step = (size_t)gridDim.x * blockDim.x;
-    for (; idx < total; idx += step) y[idx] += b[idx % (size_t)n];
+    float* row = y + (size_t)blockIdx.x * n;
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < n; i += gridDim.y * blockDim.x) row[i] += b[i];
 }
 
 MB_API int mb_add_row_bias(float* y, const float* b, int rows, int n, cudaStream_t s) {
     const size_t total = (size_t)rows * n;
     if (total == 0) return 0;
-    return launch_kernel(add_row_bias_kernel, blocks_for(total, 256), 256, 0, s, 0, y, b, total, n);
+    return launch_kernel(add_row_bias_kernel, row_grid(rows, n), 256, 0, s, 0, y, b, n);
 }
 
 // ---- RMS norm of a column block of wider rows: out[t, :] = x[t, col : col + n] / rms * w, a block per row ------------------

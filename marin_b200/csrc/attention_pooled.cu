@@ -188,27 +188,35 @@ MB_API int mb_attention_pooled(const void* q, const void* k_cache, const void* v
     return MB_ERR_BAD_DTYPE;
 }
 
-// ---- the heads' sums mixed: out[t][h][:] = sum_g talk[h][g] parts[t][g][kv(h)][:], a block per token ---------------------
+// ---- the heads' sums mixed: out[t][h][:] = sum_g talk[h][g] parts[t][g][kv(h)][:], a block per (token, kv head) -------------
+// The H rows parts[t][:][c][:] go through shared memory once (each is read by all query heads of kv head c).
 template <typename T>
 __global__ void __launch_bounds__(256) talk_mix_kernel(const float* __restrict__ parts, const float* __restrict__ talk, T* __restrict__ out,
                                                        int H, int K, int dv) {
     PDL_ENTER();
     parts = pdl_fresh(parts);
-    const int t = blockIdx.x;
-    const float* src = parts + (size_t)t * H * K * dv;
+    extern __shared__ float rows[];            // [H][dv]
+    const int t = blockIdx.x, c = blockIdx.y, group = H / K;
     for (int e = threadIdx.x; e < H * dv; e += blockDim.x) {
-        const int h = e / dv, dd = e % dv;
-        const int c = h / (H / K);
+        const int g = e / dv, dd = e - g * dv;
+        rows[e] = parts[(((size_t)t * H + g) * K + c) * dv + dd];
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < group * dv; e += blockDim.x) {
+        const int h = c * group + e / dv, dd = e % dv;
         float sum = 0.0f;
-        for (int g = 0; g < H; ++g) sum = fmaf(talk[h * H + g], src[((size_t)g * K + c) * dv + dd], sum);
-        out[(size_t)t * H * dv + e] = from_f32<T>(sum);
+        for (int g = 0; g < H; ++g) sum = fmaf(talk[h * H + g], rows[g * dv + dd], sum);
+        out[((size_t)t * H + h) * dv + dd] = from_f32<T>(sum);
     }
 }
 
 MB_API int mb_talk_mix(const float* parts, const float* talk, void* out, int dtype, int tokens, int H, int K, int dv, cudaStream_t s) {
     if (tokens <= 0) return 0;
     if (H <= 0 || K <= 0 || H % K != 0 || dv <= 0) return MB_ERR_BAD_SIZE;
-    if (dtype == MB_F32) return launch_kernel(talk_mix_kernel<float>, tokens, 256, 0, s, 0, parts, talk, (float*)out, H, K, dv);
-    if (dtype == MB_BF16) return launch_kernel(talk_mix_kernel<bf16>, tokens, 256, 0, s, 0, parts, talk, (bf16*)out, H, K, dv);
+    const size_t smem = (size_t)H * dv * sizeof(float);
+    if (smem > 48 * 1024) return MB_ERR_BAD_SIZE;
+    dim3 grid(tokens, K);
+    if (dtype == MB_F32) return launch_kernel(talk_mix_kernel<float>, grid, 256, smem, s, 0, parts, talk, (float*)out, H, K, dv);
+    if (dtype == MB_BF16) return launch_kernel(talk_mix_kernel<bf16>, grid, 256, smem, s, 0, parts, talk, (bf16*)out, H, K, dv);
     return MB_ERR_BAD_DTYPE;
 }

@@ -11,6 +11,8 @@
 // values, A[g][c] (float32 [tokens][H][K][V_DIM]), which a second kernel mixes, out_h = sum_g talk[h][g] A[g][kv(h)]; a CTA
 // then takes the kv heads c0 .. c0 + VALUE_HEADS - 1 (blockIdx.y counts (g, c0 / VALUE_HEADS)) and repeats the scores for
 // each such slice.  Without mixing a CTA sums the values of g's own kv head and writes bf16 [tokens][H][V_DIM].
+// Single tokens (`single`: every request of the step brings one token): the tile's rows are the GROUP query heads of one kv
+// head instead of 64 queries of one head (blockIdx.y counts (kv head, slice)), so the heads that share keys share their loads.
 // Scores, maxima and sums are float32 (in the exp2 domain); the weights are rounded to bf16 for the product with V.
 #define MB_LIB "attention_pooled_fast"
 #define MB_LIB_ID 19
@@ -58,7 +60,8 @@ __device__ __forceinline__ float tanh_approx(float x) {
 // [row_first, row_last] of the numbering are there, the others are zero.  pooled: row n is block n's pooled row; else position n.
 __device__ __forceinline__ void load_block(bf16* dst_k, bf16* dst_v, const bf16* __restrict__ keys, const bf16* __restrict__ values,
                                            const int* __restrict__ table, int K, int kh, int c0, int nvh, int page_shift, int row0,
-                                           int row_first, int row_last, bool pooled, int pool, int pool_rows) {
+                                           int row_first, int row_last, bool pooled, int pool, int pool_rows, int which) {
+    // which: 1 the keys, 2 the values, 3 both
     constexpr int CK = D / 8, CV = DV / 8;
     const int row = threadIdx.x >> 1, half = threadIdx.x & 1;
     const int n = row0 + row;
@@ -70,11 +73,13 @@ __device__ __forceinline__ void load_block(bf16* dst_k, bf16* dst_v, const bf16*
         const size_t per_head = pooled ? (size_t)pool_rows : ((size_t)1 << page_shift);
         const size_t at = pooled ? (size_t)((p & page_mask) / pool) : (size_t)(p & page_mask);
         const bf16* sk = keys + ((page * K + kh) * per_head + at) * D;
+        if (which & 1) {
 #pragma unroll
-        for (int c = half; c < CK; c += 2) cp_async16(dk + c * 8, sk + c * 8);
+            for (int c = half; c < CK; c += 2) cp_async16(dk + c * 8, sk + c * 8);
+        }
 #pragma unroll
         for (int v = 0; v < VH; ++v) {
-            if (v < nvh) {
+            if (v < nvh && (which & 2)) {
                 const bf16* sv = values + ((page * K + c0 + v) * per_head + at) * DV;
                 bf16* dv = dst_v + (v * BN + row) * LDV;
 #pragma unroll
@@ -82,11 +87,13 @@ __device__ __forceinline__ void load_block(bf16* dst_k, bf16* dst_v, const bf16*
             }
         }
     } else {
+        if (which & 1) {
 #pragma unroll
-        for (int c = half; c < CK; c += 2) *reinterpret_cast<uint4*>(dk + c * 8) = make_uint4(0, 0, 0, 0);
+            for (int c = half; c < CK; c += 2) *reinterpret_cast<uint4*>(dk + c * 8) = make_uint4(0, 0, 0, 0);
+        }
 #pragma unroll
         for (int v = 0; v < VH; ++v) {
-            if (v < nvh) {
+            if (v < nvh && (which & 2)) {
                 bf16* dv = dst_v + (v * BN + row) * LDV;
 #pragma unroll
                 for (int c = half; c < CV; c += 2) *reinterpret_cast<uint4*>(dv + c * 8) = make_uint4(0, 0, 0, 0);
@@ -96,27 +103,28 @@ __device__ __forceinline__ void load_block(bf16* dst_k, bf16* dst_v, const bf16*
 }
 static_assert(BN == 64, "load_block: two of the 128 threads a row");
 
-#define PF_SMEM ((BM * LDK + BN * LDK + VH * BN * LDV) * 2)
+#define PF_SMEM ((BM * LDK + 2 * BN * LDK + VH * BN * LDV) * 2)       // queries, two key blocks in turn, one block of values
 
 __global__ void __launch_bounds__(128) attn_pooled_prefill_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache, const bf16* __restrict__ k_pool,
     const bf16* __restrict__ v_pool, float* __restrict__ parts, bf16* __restrict__ out, const int* __restrict__ block_table, int max_pages,
     const int* __restrict__ cu_tokens, const int* __restrict__ seq_lens, int first_req, int K, int page_shift, float scale, float cap,
-    int window, int pool, int pool_rows, int all_heads) {
+    int window, int pool, int pool_rows, int all_heads, int single) {
     PDL_ENTER_EARLY();
     q = pdl_fresh(q); k_cache = pdl_fresh(k_cache); v_cache = pdl_fresh(v_cache); k_pool = pdl_fresh(k_pool); v_pool = pdl_fresh(v_pool);
     extern __shared__ __align__(16) uint8_t smem_raw[];
     bf16* sQ = reinterpret_cast<bf16*>(smem_raw);
-    bf16* sK = sQ + BM * LDK;
-    bf16* sV = sK + BN * LDK;
+    bf16* sK0 = sQ + BM * LDK;
+    bf16* sV = sK0 + 2 * BN * LDK;
     const int H = K * GROUP;
     const int slices = all_heads ? (K + VH - 1) / VH : 1;
-    const int r = first_req + blockIdx.z, h = blockIdx.y / slices, qt = gridDim.x - 1 - blockIdx.x;   // long tiles first
+    // (single: `h` is the first query head of the kv head, and row i of the tile is head h + i at the one position)
+    const int r = first_req + blockIdx.z, h = single ? (blockIdx.y / slices) * GROUP : blockIdx.y / slices, qt = gridDim.x - 1 - blockIdx.x;
     const int tok0 = cu_tokens[r], n = cu_tokens[r + 1] - tok0;
     if (qt * BM >= n) return;
     const int len = seq_lens[r], pos0 = len - n;
-    const int rows = min(BM, n - qt * BM);
-    const int q_first = pos0 + qt * BM, q_last = q_first + rows - 1;
+    const int rows = single ? GROUP : min(BM, n - qt * BM);
+    const int q_first = pos0 + qt * BM, q_last = single ? q_first : q_first + rows - 1;
     const int kh = h / GROUP;
     const int c0 = all_heads ? (blockIdx.y % slices) * VH : kh;
     const int nvh = all_heads ? min(VH, K - c0) : 1;
@@ -133,7 +141,7 @@ __global__ void __launch_bounds__(128) attn_pooled_prefill_kernel(
         for (int idx = threadIdx.x; idx < BM * CHUNKS; idx += 128) {
             const int row = idx / CHUNKS, c = idx % CHUNKS;
             bf16* d = sQ + row * LDK + c * 8;
-            if (row < rows) cp_async16(d, q + ((size_t)(tok0 + qt * BM + row) * H + h) * D + c * 8);
+            if (row < rows) cp_async16(d, q + (single ? (size_t)tok0 * H + h + row : (size_t)(tok0 + qt * BM + row) * H + h) * D + c * 8);
             else *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
         }
         cp_async_commit();
@@ -145,20 +153,43 @@ __global__ void __launch_bounds__(128) attn_pooled_prefill_kernel(
 #pragma unroll
         for (int i = 0; i < DV / 8; ++i) { o[v][i][0] = o[v][i][1] = o[v][i][2] = o[v][i][3] = 0.0f; }
     const int row0 = warp * 16 + (lane >> 2);                 // this thread's rows: row0 and row0 + 8
-    const int qp[2] = {q_first + row0, q_first + row0 + 8};
+    const int qp[2] = {single ? q_first : q_first + row0, single ? q_first : q_first + row0 + 8};
     const int lo[2] = {window > 0 ? max(0, qp[0] - window + 1) : 0, window > 0 ? max(0, qp[1] - window + 1) : 0};
     const int nb[2] = {pools ? max(0, (qp[0] - window + 1) / pool) : 0, pools ? max(0, (qp[1] - window + 1) / pool) : 0};
     const float inv_cap = cap > 0.0f ? 1.0f / cap : 0.0f, cap_l2 = cap * LOG2E, sl2 = scale * LOG2E;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
 
+    // The loads run ahead of the products: while block i is worked on, the keys of block i + 1 arrive in the other key buffer
+    // (asked for at the top of step i), and the values of block i + 1 are asked for as soon as step i is done with the one
+    // value buffer, so they arrive during the next step's scores.  cp.async groups complete in order: keys(i) | values(i) |
+    // keys(i + 1) | ...; "all but the newest group" is what a step waits for, twice.
+    auto fetch = [&](int step, int which) {
+        const bool pooled = step < pooled_blocks;
+        const int key0 = pooled ? step * BN : (kb_first + step - pooled_blocks) * BN;
+        bf16* dk = sK0 + (step & 1) * BN * LDK;
+        if (pooled) load_block(dk, sV, k_pool, v_pool, table, K, kh, c0, nvh, page_shift, key0, 0, nb_most - 1, true, pool, pool_rows, which);
+        else load_block(dk, sV, k_cache, v_cache, table, K, kh, c0, nvh, page_shift, key0, k_first, q_last, false, pool, pool_rows, which);
+        cp_async_commit();
+    };
+    fetch(0, 1);                                               // (the queries ride in this group's wait)
+    fetch(0, 2);
+    const bool idle = single && warp * 16 >= GROUP;            // this warp's rows hold no head: it only helps with the loads
     for (int step = 0; step < steps; ++step) {
         const bool pooled = step < pooled_blocks;
         const int key0 = pooled ? step * BN : (kb_first + step - pooled_blocks) * BN;
-        if (pooled) load_block(sK, sV, k_pool, v_pool, table, K, kh, c0, nvh, page_shift, key0, 0, nb_most - 1, true, pool, pool_rows);
-        else load_block(sK, sV, k_cache, v_cache, table, K, kh, c0, nvh, page_shift, key0, k_first, q_last, false, pool, pool_rows);
-        cp_async_commit();
-        cp_async_wait<0>();
+        const bf16* sK = sK0 + (step & 1) * BN * LDK;
+        cp_async_wait<1>();                                    // this block's keys are there (its values may still be on their way)
         __syncthreads();
+        if (step + 1 < steps) fetch(step + 1, 1);
+        else cp_async_commit();                                // (an empty group keeps the count of groups in step)
+        if (idle) {
+            cp_async_wait<1>();
+            __syncthreads();
+            __syncthreads();
+            if (step + 1 < steps) fetch(step + 1, 2);
+            else cp_async_commit();
+            continue;
+        }
         float s[BN / 8][4];
 #pragma unroll
         for (int j = 0; j < BN / 8; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f; }
@@ -217,6 +248,8 @@ __global__ void __launch_bounds__(128) attn_pooled_prefill_kernel(
             pa[ks][2] = pack_bf16(s[2 * ks + 1][0], s[2 * ks + 1][1]);
             pa[ks][3] = pack_bf16(s[2 * ks + 1][2], s[2 * ks + 1][3]);
         }
+        cp_async_wait<1>();                                    // this block's values are there
+        __syncthreads();
         // O_c += P V_c for every kv head of the slice
 #pragma unroll
         for (int v = 0; v < VH; ++v) {
@@ -236,8 +269,11 @@ __global__ void __launch_bounds__(128) attn_pooled_prefill_kernel(
                 }
             }
         }
-        __syncthreads();                                       // everyone is done with this block's buffers
+        __syncthreads();                                       // everyone is done with the value buffer
+        if (step + 1 < steps) fetch(step + 1, 2);
+        else cp_async_commit();
     }
+    cp_async_wait<0>();
     const int col = 2 * (lane & 3);
 #pragma unroll
     for (int rr = 0; rr < 2; ++rr) {
@@ -247,19 +283,20 @@ __global__ void __launch_bounds__(128) attn_pooled_prefill_kernel(
         const int row = row0 + 8 * rr;
         if (row < rows) {
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-            const size_t t = (size_t)(tok0 + qt * BM + row);
+            const size_t t = single ? (size_t)tok0 : (size_t)(tok0 + qt * BM + row);
+            const int hh = single ? h + row : h;
             if (all_heads) {
 #pragma unroll
                 for (int v = 0; v < VH; ++v) {
                     if (v < nvh) {
-                        float* dst = parts + ((t * H + h) * K + c0 + v) * DV;
+                        float* dst = parts + ((t * H + hh) * K + c0 + v) * DV;
 #pragma unroll
                         for (int i = 0; i < DV / 8; ++i)
                             *reinterpret_cast<float2*>(dst + i * 8 + col) = make_float2(o[v][i][2 * rr] * inv, o[v][i][2 * rr + 1] * inv);
                     }
                 }
             } else {
-                bf16* dst = out + (t * H + h) * DV;
+                bf16* dst = out + (t * H + hh) * DV;
 #pragma unroll
                 for (int i = 0; i < DV / 8; ++i)
                     *reinterpret_cast<uint32_t*>(dst + i * 8 + col) = pack_bf16(o[0][i][2 * rr] * inv, o[0][i][2 * rr + 1] * inv);
@@ -281,15 +318,16 @@ MB_API int mb_attn_pooled_layout(int* d, int* dv, int* group, int* value_heads) 
 MB_API int mb_attn_pooled_prefill(const void* q, const void* k_cache, const void* v_cache, const void* k_pool, const void* v_pool, float* parts,
                                   void* out, const int* block_table, int max_pages, const int* cu_tokens, const int* seq_lens, int first_req,
                                   int count, int max_query_len, int K, int page_size, float scale, float cap, int window, int pool,
-                                  int pool_rows, int all_heads, cudaStream_t s) {
+                                  int pool_rows, int all_heads, int single, cudaStream_t s) {
     if (count <= 0 || max_query_len <= 0) return 0;
     const int shift = page_shift_of(page_size);
     if (shift < 0 || window < 0 || pool < 0 || (pool > 0 && (k_pool == nullptr || v_pool == nullptr))) return MB_ERR_BAD_SIZE;
     if (pool > 0 && pool_rows != (page_size + pool - 1) / pool) return MB_ERR_BAD_SIZE;
     cudaFuncSetAttribute(attn_pooled_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM);
     const int slices = all_heads ? (K + VH - 1) / VH : 1;
-    dim3 grid((max_query_len + BM - 1) / BM, K * GROUP * slices, count);
+    if (single && (max_query_len != 1 || GROUP > 16)) single = 0;
+    dim3 grid((max_query_len + BM - 1) / BM, (single ? K : K * GROUP) * slices, count);
     return launch_kernel(attn_pooled_prefill_kernel, grid, 128, PF_SMEM, s, 0, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
                          (const bf16*)k_pool, (const bf16*)v_pool, parts, (bf16*)out, block_table, max_pages, cu_tokens, seq_lens, first_req, K,
-                         shift, scale, cap, window, pool, pool_rows, all_heads);
+                         shift, scale, cap, window, pool, pool_rows, all_heads, single);
 }

@@ -100,11 +100,20 @@ MB_API int mb_ssm_conv_carry(const void* in, int in_stride, int in_col, int dtyp
 #define SS_THREADS (SS_COLS * 4)
 #define SS_RUN 16
 
+// mode 0: a request's tokens of the step in one walk, from its state slot and back into it.
+// Long portions are cut into segments of `seg_len` tokens that are walked side by side (the recurrence is linear in the state):
+// mode 1: every segment from a zero state, no outputs; its end state goes to seg_state[segment] and the product of its decays
+//         to seg_decay[segment][head];
+// (ssm_combine_kernel then turns the end states into the segments' start states, S <- decay_b S + end_b, segment after segment
+//  from the slot's state, and leaves the last one in the slot;)
+// mode 2: every segment again from its start state, for the outputs.
+// blockIdx.x = request * segments + segment (one segment in mode 0).
 template <typename T, int ROWS>
 __global__ void __launch_bounds__(SS_THREADS) ssm_scan_kernel(
     const T* __restrict__ xbc, const T* __restrict__ dt_rows, int dt_stride, int dt_col, const float* __restrict__ dt_bias,
     const float* __restrict__ rate_log, const float* __restrict__ skip, float* __restrict__ state, const int* __restrict__ cu_tokens,
-    const int* __restrict__ slots, float* __restrict__ y, int heads, int P, int N, int groups) {
+    const int* __restrict__ slots, float* __restrict__ y, int heads, int P, int N, int groups, int mode, int segments, int seg_len,
+    float* __restrict__ seg_state, float* __restrict__ seg_decay) {
     PDL_ENTER();
     xbc = pdl_fresh(xbc); dt_rows = pdl_fresh(dt_rows);
     extern __shared__ float smem[];
@@ -112,22 +121,29 @@ __global__ void __launch_bounds__(SS_THREADS) ssm_scan_kernel(
     float* Cs = Bs + SS_RUN * N;               // [SS_RUN][N]
     float* xs = Cs + SS_RUN * N;               // [SS_RUN][SS_COLS]
     float* steps = xs + SS_RUN * SS_COLS;      // [SS_RUN] dt, [SS_RUN] decay
-    const int req = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * SS_COLS;
-    const int first = cu_tokens[req], count = cu_tokens[req + 1] - first;
-    if (count <= 0) return;
+    const int req = blockIdx.x / segments, seg = blockIdx.x - req * segments;
+    const int head = blockIdx.y, col0 = blockIdx.z * SS_COLS;
+    int first = cu_tokens[req], count = cu_tokens[req + 1] - first;
+    if (mode != 0) {
+        first += seg * seg_len;
+        count = max(0, min(seg_len, count - seg * seg_len));
+    }
+    if (count <= 0 && mode != 1) return;
     const int inner = heads * P, channels = inner + 2 * groups * N;
     const int g = head / (heads / groups);
     const int col = threadIdx.x >> 2, part = threadIdx.x & 3;
     const int p = col0 + col;
     const bool in_range = p < P;
-    float* S = state + (((size_t)slots[req] * heads + head) * N) * P;
+    float* S = mode == 0 ? state + (((size_t)slots[req] * heads + head) * N) * P
+                         : seg_state + (((size_t)blockIdx.x * heads + head) * N) * P;
     float s[ROWS];
 #pragma unroll
     for (int j = 0; j < ROWS; ++j) {
         const int n = part + 4 * j;
-        s[j] = (in_range && n < N) ? S[(size_t)n * P + p] : 0.0f;
+        s[j] = (mode != 1 && in_range && n < N) ? S[(size_t)n * P + p] : 0.0f;
     }
     const float rate = expf(rate_log[head]), bias = dt_bias[head], d_skip = skip[head];
+    float log_decay = 0.0f;
     for (int base = 0; base < count; base += SS_RUN) {
         const int run = min(SS_RUN, count - base);
         __syncthreads();
@@ -144,27 +160,32 @@ __global__ void __launch_bounds__(SS_THREADS) ssm_scan_kernel(
         if (threadIdx.x < run) {
             const float dt = softplus_f(to_f32(dt_rows[(size_t)(first + base + threadIdx.x) * dt_stride + dt_col + head]) + bias);
             steps[threadIdx.x] = dt;
-            steps[SS_RUN + threadIdx.x] = expf(-rate * dt);
+            steps[SS_RUN + threadIdx.x] = -rate * dt;
         }
         __syncthreads();
         for (int tt = 0; tt < run; ++tt) {
-            const float dt = steps[tt], a = steps[SS_RUN + tt];
+            const float dt = steps[tt], a = expf(steps[SS_RUN + tt]);
+            log_decay += steps[SS_RUN + tt];
             const float x = xs[tt * SS_COLS + col];
             const float dx = dt * x;
-            float sum = 0.0f;
+            float sums[4] = {0.0f, 0.0f, 0.0f, 0.0f};                      // four chains instead of one of ROWS dependent sums
 #pragma unroll
             for (int j = 0; j < ROWS; ++j) {
                 const int n = part + 4 * j;
                 if (n < N) {
                     s[j] = fmaf(a, s[j], dx * Bs[tt * N + n]);
-                    sum = fmaf(s[j], Cs[tt * N + n], sum);
+                    sums[j & 3] = fmaf(s[j], Cs[tt * N + n], sums[j & 3]);
                 }
             }
-            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-            if (part == 0 && in_range) y[(size_t)(first + base + tt) * inner + head * P + p] = fmaf(d_skip, x, sum);
+            float sum = (sums[0] + sums[1]) + (sums[2] + sums[3]);
+            if (mode != 1) {
+                sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+                sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+                if (part == 0 && in_range) y[(size_t)(first + base + tt) * inner + head * P + p] = fmaf(d_skip, x, sum);
+            }
         }
     }
+    if (mode == 2) return;
     if (in_range) {
 #pragma unroll
         for (int j = 0; j < ROWS; ++j) {
@@ -172,37 +193,64 @@ __global__ void __launch_bounds__(SS_THREADS) ssm_scan_kernel(
             if (n < N) S[(size_t)n * P + p] = s[j];
         }
     }
+    if (mode == 1 && threadIdx.x == 0 && blockIdx.z == 0) seg_decay[(size_t)blockIdx.x * heads + head] = expf(log_decay);
+}
+
+// The segments' end states turned into their start states, in place: a block per (request, head).
+__global__ void __launch_bounds__(256) ssm_combine_kernel(float* __restrict__ state, const int* __restrict__ slots, float* __restrict__ seg_state,
+                                                          const float* __restrict__ seg_decay, int heads, int elems, int segments) {
+    PDL_ENTER();
+    const int req = blockIdx.x, head = blockIdx.y;
+    float* S = state + ((size_t)slots[req] * heads + head) * elems;
+    for (int e = threadIdx.x; e < elems; e += blockDim.x) {
+        float v = S[e];
+        for (int b = 0; b < segments; ++b) {
+            const size_t at = (size_t)req * segments + b;
+            float* slot = seg_state + (at * heads + head) * elems + e;
+            const float end = *slot;
+            *slot = v;
+            v = fmaf(seg_decay[at * heads + head], v, end);
+        }
+        S[e] = v;
+    }
 }
 
 template <typename T>
 static int ssm_scan_rows(int rows, dim3 grid, size_t smem, cudaStream_t s, const T* xbc, const T* dt_rows, int dt_stride, int dt_col,
                          const float* dt_bias, const float* rate_log, const float* skip, float* state, const int* cu_tokens, const int* slots,
-                         float* y, int heads, int P, int N, int groups) {
+                         float* y, int heads, int P, int N, int groups, int mode, int segments, int seg_len, float* seg_state, float* seg_decay) {
 #define SS_CASE(R)                                                                                                                   \
     if (rows <= R)                                                                                                                   \
         return launch_kernel(ssm_scan_kernel<T, R>, grid, SS_THREADS, smem, s, 0, xbc, dt_rows, dt_stride, dt_col, dt_bias, rate_log, skip, \
-                             state, cu_tokens, slots, y, heads, P, N, groups);
+                             state, cu_tokens, slots, y, heads, P, N, groups, mode, segments, seg_len, seg_state, seg_decay);
     SS_CASE(4) SS_CASE(8) SS_CASE(16) SS_CASE(32) SS_CASE(64)
 #undef SS_CASE
     return MB_ERR_BAD_SIZE;
 }
 
 // xbc: [tokens][heads P + 2 groups N] after the convolution; dt_rows: the projection's rows, dt' of head h at column dt_col + h.
+// mode 0 with segments = 1: one walk per request.  Modes 1 and 2 (see the kernel): `segments` segments of seg_len tokens a request,
+// seg_state float32 [requests][segments][heads][N][P], seg_decay [requests][segments][heads]; mode 3: the combining step between them.
 MB_API int mb_ssm_scan(const void* xbc, const void* dt_rows, int dt_stride, int dt_col, int dtype, const float* dt_bias, const float* rate_log,
                        const float* skip, float* state, const int* cu_tokens, const int* slots, float* y, int requests, int heads, int P, int N,
-                       int groups, cudaStream_t s) {
+                       int groups, int mode, int segments, int seg_len, float* seg_state, float* seg_decay, cudaStream_t s) {
     if (requests <= 0) return 0;
-    if (heads <= 0 || P <= 0 || N <= 0 || N > 256 || groups <= 0 || heads % groups != 0) return MB_ERR_BAD_SIZE;
-    dim3 grid(requests, heads, (P + SS_COLS - 1) / SS_COLS);
+    if (heads <= 0 || P <= 0 || N <= 0 || N > 256 || groups <= 0 || heads % groups != 0 || mode < 0 || mode > 3) return MB_ERR_BAD_SIZE;
+    if (mode == 0) segments = 1;
+    if (segments <= 0 || (mode != 0 && (seg_len <= 0 || seg_state == nullptr || seg_decay == nullptr))) return MB_ERR_BAD_SIZE;
+    if (mode == 3)
+        return launch_kernel(ssm_combine_kernel, dim3(requests, heads), 256, 0, s, 0, state, slots, seg_state, (const float*)seg_decay, heads,
+                             N * P, segments);
+    dim3 grid(requests * segments, heads, (P + SS_COLS - 1) / SS_COLS);
     const size_t smem = (size_t)(2 * SS_RUN * N + SS_RUN * SS_COLS + 2 * SS_RUN) * sizeof(float);
     if (smem > 48 * 1024) return MB_ERR_BAD_SIZE;
     const int rows = (N + 3) / 4;
     if (dtype == MB_F32)
         return ssm_scan_rows<float>(rows, grid, smem, s, (const float*)xbc, (const float*)dt_rows, dt_stride, dt_col, dt_bias, rate_log, skip,
-                                    state, cu_tokens, slots, y, heads, P, N, groups);
+                                    state, cu_tokens, slots, y, heads, P, N, groups, mode, segments, seg_len, seg_state, seg_decay);
     if (dtype == MB_BF16)
         return ssm_scan_rows<bf16>(rows, grid, smem, s, (const bf16*)xbc, (const bf16*)dt_rows, dt_stride, dt_col, dt_bias, rate_log, skip,
-                                   state, cu_tokens, slots, y, heads, P, N, groups);
+                                   state, cu_tokens, slots, y, heads, P, N, groups, mode, segments, seg_len, seg_state, seg_decay);
     return MB_ERR_BAD_DTYPE;
 }
 

@@ -1708,18 +1708,19 @@ def attention_pooled(q, k_cache, v_cache, k_pool, v_pool, out, ctx, block_table,
     pair_flops = 2.0 * H * (d + (K if talk is not None else 1) * dv)
     plain_tokens = T
     if use_fast_pooled_attention and fast_pooled_attention_supported(q.dtype, H, K, d, dv) and page_size & (page_size - 1) == 0:
-        # prompt portions on the tensor cores; the single tokens (the step's first rows) stay with the plain kernel
-        plain_tokens = nd = ctx.num_decode
-        if ctx.num_requests > nd:
-            if launch_log is not None:
-                _cost((T - nd) * H * (d + dv) * size, 0.0, K * (d + dv) * size, pair_flops)
-                _pending_cost["rows"], _pending_cost["window"] = "prefill", window
-            lib = _pooled_lib(d, dv, H // K, pooled_value_heads(K, dv))
-            _check(lib.mb_attn_pooled_prefill(
-                _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(k_pool), _ptr(v_pool), _ptr(parts), _ptr(out), _ptr(block_table),
-                _c_int(block_table.shape[1]), _ptr(ctx.cu_tokens), _ptr(ctx.seq_lens), _c_int(nd), _c_int(ctx.num_requests - nd),
-                _c_int(ctx.max_query_len), _c_int(K), _c_int(page_size), _c_float(scale), _c_float(softcap or 0.0), _c_int(window), _c_int(pool),
-                _c_int(rows), _c_int(int(talk is not None)), _stream()), "attention (window and pooled blocks, prefill, tensor cores)")
+        # the tensor-core kernel takes every request of the step: a prompt portion in tiles of 64 queries, a single token as a
+        # tile of one (the plain kernel walks a token's keys in one block of threads, far too slowly for a window of a thousand)
+        plain_tokens = 0
+        if launch_log is not None:
+            _cost(T * H * (d + dv) * size, 0.0, K * (d + dv) * size, pair_flops)
+            _pending_cost["rows"], _pending_cost["window"] = "all", window
+        lib = _pooled_lib(d, dv, H // K, pooled_value_heads(K, dv))
+        _check(lib.mb_attn_pooled_prefill(
+            _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(k_pool), _ptr(v_pool), _ptr(parts), _ptr(out), _ptr(block_table),
+            _c_int(block_table.shape[1]), _ptr(ctx.cu_tokens), _ptr(ctx.seq_lens), _c_int(0), _c_int(ctx.num_requests),
+            _c_int(ctx.max_query_len), _c_int(K), _c_int(page_size), _c_float(scale), _c_float(softcap or 0.0), _c_int(window), _c_int(pool),
+            _c_int(rows), _c_int(int(talk is not None)), _c_int(int(ctx.max_query_len == 1 and ctx.num_decode == ctx.num_requests)), _stream()),
+            "attention (window and pooled blocks, tensor cores)")
     if plain_tokens > 0:
         if launch_log is not None:
             _cost(plain_tokens * H * (d + dv) * size, 0.0, K * (d + dv) * size, pair_flops)
@@ -1805,10 +1806,34 @@ def ssm_scan(xbc: torch.Tensor, rows: torch.Tensor, dt_col: int, dt_bias: torch.
     assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, N, P)
     assert y.dtype == torch.float32 and tuple(y.shape) == (T, heads * P) and dt_bias.dtype == rate_log.dtype == skip.dtype == torch.float32
     R = ctx.num_requests
+    lib = _lib("mb_ssm")
+
+    def run(mode, segments, seg_len, seg_state, seg_decay, what):
+        _check(lib.mb_ssm_scan(_ptr(xbc), _ptr(rows), _c_int(rows.stride(0)), _c_int(dt_col), _code(xbc), _ptr(dt_bias), _ptr(rate_log), _ptr(skip),
+                               _ptr(state), _ptr(ctx.cu_tokens), _ptr(slots), _ptr(y), _c_int(R), _c_int(heads), _c_int(P), _c_int(N), _c_int(groups),
+                               _c_int(mode), _c_int(segments), _c_int(seg_len), _ptr(seg_state), _ptr(seg_decay), _stream()), what)
+
+    longest = ctx.max_query_len
+    if xbc.dtype == torch.bfloat16 and longest >= SSM_SEGMENTS_FROM and not torch.cuda.is_current_stream_capturing():
+        # long portions in segments walked side by side: end states and decay products from zero, the start states from those,
+        # then the outputs (float32 mode keeps the one walk: its sums must not depend on how a prompt was cut)
+        segments = -(-longest // SSM_SEGMENT_TOKENS)
+        seg_state = ctx.workspace.get("ssm_segment_states", (R, segments, heads, N, P), torch.float32)
+        seg_decay = ctx.workspace.get("ssm_segment_decays", (R, segments, heads), torch.float32)
+        _cost(_size(xbc) + 2 * _size(seg_state), 4.0 * T * heads * N * P)
+        run(1, segments, SSM_SEGMENT_TOKENS, seg_state, seg_decay, "state space recurrence (segments' end states)")
+        _cost(2 * _size(seg_state) + 2 * R * heads * N * P * 4, 2.0 * _size(seg_state) / 4)
+        run(3, segments, SSM_SEGMENT_TOKENS, seg_state, seg_decay, "state space recurrence (segments' start states)")
+        _cost(_size(xbc) + _size(y) + _size(seg_state), 6.0 * T * heads * N * P)
+        run(2, segments, SSM_SEGMENT_TOKENS, seg_state, seg_decay, "state space recurrence (segments' outputs)")
+        return
     _cost(_size(xbc) + _size(y) + 2 * R * heads * N * P * 4, 6.0 * T * heads * N * P)
-    _check(_lib("mb_ssm").mb_ssm_scan(_ptr(xbc), _ptr(rows), _c_int(rows.stride(0)), _c_int(dt_col), _code(xbc), _ptr(dt_bias), _ptr(rate_log),
-                                     _ptr(skip), _ptr(state), _ptr(ctx.cu_tokens), _ptr(slots), _ptr(y), _c_int(R), _c_int(heads), _c_int(P),
-                                     _c_int(N), _c_int(groups), _stream()), "state space recurrence")
+    run(0, 1, 0, None, None, "state space recurrence")
+
+
+#: portions from this many tokens on are walked in segments side by side (bf16 mode), of so many tokens each
+SSM_SEGMENTS_FROM = 256
+SSM_SEGMENT_TOKENS = 128
 
 
 def ssm_gate_norm(y: torch.Tensor, rows: torch.Tensor, z_col: int, weight: torch.Tensor, eps: float, parts: int, out: torch.Tensor) -> None:

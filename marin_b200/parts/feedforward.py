@@ -186,7 +186,7 @@ class CappedGLU(FeedForward):
         if self.scaled:
             parts.append(tensors.pop(self.scale_name).reshape(1, self.hidden))
             # (rows up to a multiple of 8, so that every product kernel takes the matrix)
-            parts.append(torch.zeros((-(2 * self.intermediate + 1)) % 8, self.hidden, dtype=parts[0].dtype))
+            parts.append(torch.zeros((-(2 * self.intermediate + 1)) % 8, self.hidden, dtype=parts[0].dtype, device=parts[0].device))
         self.w_in = rt.matrix(torch.cat(parts, dim=0))
         self.w_down = rt.matrix(tensors.pop(self.down_name))
 
