@@ -50,10 +50,10 @@ __device__ __forceinline__ float ex2_approx(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// tanh(x) = 1 - 2 / (1 + e^(2x)) from the fast exponential: its absolute error is a few 1e-7, which times the cap stays far below
+// a score's rounding (the hardware's own tanh approximation is good to 2^-11 only, times a cap of 50 a visible 0.01 in a score)
 __device__ __forceinline__ float tanh_approx(float x) {
-    float y;
-    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
+    return 1.0f - __fdividef(2.0f, 1.0f + ex2_approx(x * (2.0f * LOG2E)));
 }
 
 // One 64-row block of keys (kv head kh) and of the values of `nvh` kv heads from c0 on (cp.async), two threads a row.  Rows

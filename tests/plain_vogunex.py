@@ -1,8 +1,8 @@
 """A plain, slow implementation of Vogunex in float64: one function per mechanism, whole sequences only, no cache, no
 batch.  It shares nothing with the package; the GPU tests compare the engine with it.
 
-``config`` is the dictionary of a model's ``config.json``; ``tensors`` maps tensor names to float64 tensors (the router's
-integer-free design has no integer tables).  Matrices are stored ``[out, in]``.
+``config`` is the dictionary of a model's ``config.json``; ``tensors`` maps tensor names to float64 tensors.  Matrices are
+stored ``[out, in]``.
 """
 from __future__ import annotations
 

@@ -119,3 +119,54 @@ def test_a_random_vogunex_configuration(tmp_path, seed, dtype):
     for rid in tokens:
         same(got[rid], rid, "in a mixed batch")
     r.cache.check()
+
+
+# Sizes nearer a real model's: wide heads, many experts, a latent wider than any tensor-core kernel takes (its attention runs the
+# plain kernels), a state of 128 rows, sixteen heads on four kv heads, a pool larger than a page.
+LARGER = {
+    "architecture": "Vogunex", "vocab": 1000, "width": 512, "embedding": {"scale": 20.0}, "norm": {"eps": 1e-5},
+    "layers": [
+        {"type": "mamba2", "mixer": _ssm(16, 64, 128, 2, 4, 4), "mlp": _moe(256, 32, 8, 2.0, shared=512, shared_limit=4.0)},
+        {"type": "attention", "mixer": _attn(16, 4, 128, 128, 3.0 / math.sqrt(128), size=90, pool=24, rot={"base": 1000000.0, "dims": 128}, softcap=20.0),
+         "mlp": _dense(1024)},
+        {"type": "latent_attention", "mixer": _latent(16, 128, 64, 128, 512, 384, 1.0 / math.sqrt(192), 10000.0, size=50), "mlp": _moe(128, 6, 2, 1.0)},
+        {"type": "attention", "mixer": _attn(16, 4, 128, 128, 3.0 / math.sqrt(128), size=90, pool=24, rot={"base": 1000000.0, "dims": 128}, softcap=20.0),
+         "mlp": _dense(1024), "weights_of": 1},
+        {"type": "latent_attention", "mixer": _latent(8, 64, 32, 64, 128, 256, 1.0 / math.sqrt(96), 10000.0), "mlp": None},
+    ],
+}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_larger_vogunex_configuration(tmp_path, dtype):
+    from marin_b200.cache import CacheManager
+    from marin_b200.engine import Runner, load_model
+
+    raw = LARGER
+    d = write_model(str(tmp_path / "m"), raw, random_weights(raw, 5))
+    w = plain.read_weights(d)
+    rng = random.Random(77)
+    lengths = {"a": 170, "b": 3, "c": 65}
+    tokens = {rid: random_prompt(rng, raw["vocab"], n) for rid, n in lengths.items()}
+    want, safe = {}, {}
+    for rid, t in tokens.items():
+        margins = []
+        want[rid] = plain.forward(raw, w, t, None, margins)
+        tight = torch.stack(margins).min(dim=0).values < 0.1
+        safe[rid] = int(torch.nonzero(tight)[0]) if bool(tight.any()) else len(t)
+    rt = runtime(dtype)
+    _, model = load_model(d, rt)
+    cache = CacheManager(model.cache_needs(), [e.cache_of for e in model.spec.schedule], PAGE, 40, 4)
+    cache.allocate(rt.device, rt.dtype)
+    r = Runner(model, cache, rt, 512)
+    r.enable_graphs((1, 2, 4))
+
+    def same(got, rid, how):
+        close(got, want[rid], dtype, f"larger, {rid} {how}", 0.02 if dtype == "bfloat16" else 0.0, safe[rid], 0.1, 0.04)
+
+    same(run_whole(r, "a", tokens["a"]), "a", "whole")
+    same(run_portions(r, "at", tokens["a"], [120] + [1] * 50), "a", "with a decoded tail")
+    got = run_mixed(r, tokens, mixed_schedule(random.Random(1), lengths, max_live=3, decode_tail=8))
+    for rid in tokens:
+        same(got[rid], rid, "in a mixed batch")
+    r.cache.check()
