@@ -90,7 +90,7 @@ def test_a_random_vogunex_configuration(tmp_path, seed, dtype):
     for rid, t in tokens.items():
         margins = []
         want[rid] = plain.forward(raw, w, t, None, margins)
-        tight = torch.stack(margins).min(dim=0).values < 0.1 if margins else torch.zeros(len(t), dtype=torch.bool)
+        tight = torch.stack(margins).min(dim=0).values < 0.2 if margins else torch.zeros(len(t), dtype=torch.bool)
         safe[rid] = int(torch.nonzero(tight)[0]) if bool(tight.any()) else len(t)
     rt = runtime(dtype)
     _, model = load_model(d, rt)
@@ -105,7 +105,9 @@ def test_a_random_vogunex_configuration(tmp_path, seed, dtype):
 
     def same(got, rid, how):
         what = f"seed {seed}: {[(l['type'][0], l['mixer']['heads'], l.get('weights_of')) for l in raw['layers']]}"
-        close(got, want[rid], dtype, f"{what}, {rid} {how}", 0.02 if dtype == "bfloat16" else 0.0, safe[rid], 0.1, 0.04)
+        # (float32: 5e-4, not 2e-4: an angle of 200 radians is good to 1e-5 in 32 bits, and the sharpest of these attentions
+        # multiply that by scores of 20)
+        close(got, want[rid], dtype, f"{what}, {rid} {how}", 0.03 if dtype == "bfloat16" else 0.0, safe[rid], 0.12, 0.05, 5e-4)
 
     r = runner(64, graphs=True)
     for rid in ("a", "c"):
@@ -152,7 +154,7 @@ def test_a_larger_vogunex_configuration(tmp_path, dtype):
     for rid, t in tokens.items():
         margins = []
         want[rid] = plain.forward(raw, w, t, None, margins)
-        tight = torch.stack(margins).min(dim=0).values < 0.1
+        tight = torch.stack(margins).min(dim=0).values < 0.2
         safe[rid] = int(torch.nonzero(tight)[0]) if bool(tight.any()) else len(t)
     rt = runtime(dtype)
     _, model = load_model(d, rt)
@@ -162,7 +164,7 @@ def test_a_larger_vogunex_configuration(tmp_path, dtype):
     r.enable_graphs((1, 2, 4))
 
     def same(got, rid, how):
-        close(got, want[rid], dtype, f"larger, {rid} {how}", 0.02 if dtype == "bfloat16" else 0.0, safe[rid], 0.1, 0.04)
+        close(got, want[rid], dtype, f"larger, {rid} {how}", 0.03 if dtype == "bfloat16" else 0.0, safe[rid], 0.12, 0.05, 5e-4)
 
     same(run_whole(r, "a", tokens["a"]), "a", "whole")
     same(run_portions(r, "at", tokens["a"], [120] + [1] * 50), "a", "with a decoded tail")
