@@ -13,6 +13,9 @@
 // each such slice.  Without mixing a CTA sums the values of g's own kv head and writes bf16 [tokens][H][V_DIM].
 // Single tokens (`single`: every request of the step brings one token): the tile's rows are the GROUP query heads of one kv
 // head instead of 64 queries of one head (blockIdx.y counts (kv head, slice)), so the heads that share keys share their loads.
+// `single` = 2 (mixing, at most four slices): a CTA takes a kv head's query heads with *all* slices, warp w working out the
+// sums of slice w over the one copy of the keys (the scores are cheap enough to repeat per warp); the value buffer then holds
+// every kv head's block.
 // Scores, maxima and sums are float32 (in the exp2 domain); the weights are rounded to bf16 for the product with V.
 #define MB_LIB "attention_pooled_fast"
 #define MB_LIB_ID 19
@@ -86,6 +89,14 @@ __device__ __forceinline__ void load_block(bf16* dst_k, bf16* dst_v, const bf16*
                 for (int c = half; c < CV; c += 2) cp_async16(dv + c * 8, sv + c * 8);
             }
         }
+        for (int v = VH; v < nvh; ++v) {                  // (a CTA that holds every kv head's block: the heads beyond a slice)
+            if (which & 2) {
+                const bf16* sv = values + ((page * K + c0 + v) * per_head + at) * DV;
+                bf16* dv = dst_v + (v * BN + row) * LDV;
+#pragma unroll
+                for (int c = half; c < CV; c += 2) cp_async16(dv + c * 8, sv + c * 8);
+            }
+        }
     } else {
         if (which & 1) {
 #pragma unroll
@@ -94,6 +105,13 @@ __device__ __forceinline__ void load_block(bf16* dst_k, bf16* dst_v, const bf16*
 #pragma unroll
         for (int v = 0; v < VH; ++v) {
             if (v < nvh && (which & 2)) {
+                bf16* dv = dst_v + (v * BN + row) * LDV;
+#pragma unroll
+                for (int c = half; c < CV; c += 2) *reinterpret_cast<uint4*>(dv + c * 8) = make_uint4(0, 0, 0, 0);
+            }
+        }
+        for (int v = VH; v < nvh; ++v) {
+            if (which & 2) {
                 bf16* dv = dst_v + (v * BN + row) * LDV;
 #pragma unroll
                 for (int c = half; c < CV; c += 2) *reinterpret_cast<uint4*>(dv + c * 8) = make_uint4(0, 0, 0, 0);
@@ -119,17 +137,21 @@ __global__ void __launch_bounds__(128) attn_pooled_prefill_kernel(
     const int H = K * GROUP;
     const int slices = all_heads ? (K + VH - 1) / VH : 1;
     // (single: `h` is the first query head of the kv head, and row i of the tile is head h + i at the one position)
-    const int r = first_req + blockIdx.z, h = single ? (blockIdx.y / slices) * GROUP : blockIdx.y / slices, qt = gridDim.x - 1 - blockIdx.x;
+    const bool by_warp = single == 2;                        // every slice in this CTA, a warp each
+    const int per_y = by_warp ? 1 : slices;
+    const int r = first_req + blockIdx.z, h = single ? (blockIdx.y / per_y) * GROUP : blockIdx.y / per_y, qt = gridDim.x - 1 - blockIdx.x;
     const int tok0 = cu_tokens[r], n = cu_tokens[r + 1] - tok0;
     if (qt * BM >= n) return;
     const int len = seq_lens[r], pos0 = len - n;
     const int rows = single ? GROUP : min(BM, n - qt * BM);
     const int q_first = pos0 + qt * BM, q_last = single ? q_first : q_first + rows - 1;
     const int kh = h / GROUP;
-    const int c0 = all_heads ? (blockIdx.y % slices) * VH : kh;
-    const int nvh = all_heads ? min(VH, K - c0) : 1;
-    const int* table = block_table + (size_t)r * max_pages;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // c0, nvh: the kv heads whose values this warp sums; load_c0, load_n: those the CTA's value buffer holds
+    const int c0 = by_warp ? min(warp, slices - 1) * VH : all_heads ? (blockIdx.y % slices) * VH : kh;
+    const int nvh = all_heads ? min(VH, K - c0) : 1;
+    const int load_c0 = by_warp ? 0 : c0, load_n = by_warp ? K : nvh;
+    const int* table = block_table + (size_t)r * max_pages;
     const int k_first = window > 0 ? max(0, q_first - window + 1) : 0;
     const int kb_first = k_first / BN, kb_last = q_last / BN;
     const bool pools = pool > 0 && window > 0;
@@ -146,13 +168,14 @@ __global__ void __launch_bounds__(128) attn_pooled_prefill_kernel(
         }
         cp_async_commit();
     }
-    const uint32_t q_addr = (uint32_t)__cvta_generic_to_shared(sQ + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDK + (lane >> 4) * 8);
+    const int tile_row = by_warp ? 0 : warp * 16;            // (by warp: every warp works on the one tile of GROUP heads)
+    const uint32_t q_addr = (uint32_t)__cvta_generic_to_shared(sQ + (tile_row + (lane & 7) + ((lane >> 3) & 1) * 8) * LDK + (lane >> 4) * 8);
     float o[VH][DV / 8][4];
 #pragma unroll
     for (int v = 0; v < VH; ++v)
 #pragma unroll
         for (int i = 0; i < DV / 8; ++i) { o[v][i][0] = o[v][i][1] = o[v][i][2] = o[v][i][3] = 0.0f; }
-    const int row0 = warp * 16 + (lane >> 2);                 // this thread's rows: row0 and row0 + 8
+    const int row0 = tile_row + (lane >> 2);                  // this thread's rows: row0 and row0 + 8
     const int qp[2] = {single ? q_first : q_first + row0, single ? q_first : q_first + row0 + 8};
     const int lo[2] = {window > 0 ? max(0, qp[0] - window + 1) : 0, window > 0 ? max(0, qp[1] - window + 1) : 0};
     const int nb[2] = {pools ? max(0, (qp[0] - window + 1) / pool) : 0, pools ? max(0, (qp[1] - window + 1) / pool) : 0};
@@ -167,13 +190,14 @@ __global__ void __launch_bounds__(128) attn_pooled_prefill_kernel(
         const bool pooled = step < pooled_blocks;
         const int key0 = pooled ? step * BN : (kb_first + step - pooled_blocks) * BN;
         bf16* dk = sK0 + (step & 1) * BN * LDK;
-        if (pooled) load_block(dk, sV, k_pool, v_pool, table, K, kh, c0, nvh, page_shift, key0, 0, nb_most - 1, true, pool, pool_rows, which);
-        else load_block(dk, sV, k_cache, v_cache, table, K, kh, c0, nvh, page_shift, key0, k_first, q_last, false, pool, pool_rows, which);
+        if (pooled) load_block(dk, sV, k_pool, v_pool, table, K, kh, load_c0, load_n, page_shift, key0, 0, nb_most - 1, true, pool, pool_rows, which);
+        else load_block(dk, sV, k_cache, v_cache, table, K, kh, load_c0, load_n, page_shift, key0, k_first, q_last, false, pool, pool_rows, which);
         cp_async_commit();
     };
     fetch(0, 1);                                               // (the queries ride in this group's wait)
     fetch(0, 2);
-    const bool idle = single && warp * 16 >= GROUP;            // this warp's rows hold no head: it only helps with the loads
+    // a warp whose rows hold no head (or, by warp, that has no slice) only helps with the loads
+    const bool idle = by_warp ? warp >= slices : (single && warp * 16 >= GROUP);
     for (int step = 0; step < steps; ++step) {
         const bool pooled = step < pooled_blocks;
         const int key0 = pooled ? step * BN : (kb_first + step - pooled_blocks) * BN;
@@ -256,7 +280,7 @@ __global__ void __launch_bounds__(128) attn_pooled_prefill_kernel(
             if (v < nvh) {
 #pragma unroll
                 for (int i = 0; i < DV / 8; ++i) { o[v][i][0] *= corr[0]; o[v][i][1] *= corr[0]; o[v][i][2] *= corr[1]; o[v][i][3] *= corr[1]; }
-                const uint32_t v_addr = (uint32_t)__cvta_generic_to_shared(sV + (v * BN + (lane & 7) + ((lane >> 3) & 1) * 8) * LDV + (lane >> 4) * 8);
+                const uint32_t v_addr = (uint32_t)__cvta_generic_to_shared(sV + ((c0 - load_c0 + v) * BN + (lane & 7) + ((lane >> 3) & 1) * 8) * LDV + (lane >> 4) * 8);
 #pragma unroll
                 for (int ks = 0; ks < BN / 16; ++ks) {
 #pragma unroll
@@ -281,7 +305,7 @@ __global__ void __launch_bounds__(128) attn_pooled_prefill_kernel(
         l += __shfl_xor_sync(0xffffffffu, l, 1);
         l += __shfl_xor_sync(0xffffffffu, l, 2);
         const int row = row0 + 8 * rr;
-        if (row < rows) {
+        if (row < rows && !idle) {
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
             const size_t t = single ? (size_t)tok0 : (size_t)(tok0 + qt * BM + row);
             const int hh = single ? h + row : h;
@@ -318,16 +342,26 @@ MB_API int mb_attn_pooled_layout(int* d, int* dv, int* group, int* value_heads) 
 MB_API int mb_attn_pooled_prefill(const void* q, const void* k_cache, const void* v_cache, const void* k_pool, const void* v_pool, float* parts,
                                   void* out, const int* block_table, int max_pages, const int* cu_tokens, const int* seq_lens, int first_req,
                                   int count, int max_query_len, int K, int page_size, float scale, float cap, int window, int pool,
-                                  int pool_rows, int all_heads, int single, cudaStream_t s) {
+                                  int pool_rows, int all_heads, int single, int by_warp_from, cudaStream_t s) {
     if (count <= 0 || max_query_len <= 0) return 0;
     const int shift = page_shift_of(page_size);
     if (shift < 0 || window < 0 || pool < 0 || (pool > 0 && (k_pool == nullptr || v_pool == nullptr))) return MB_ERR_BAD_SIZE;
     if (pool > 0 && pool_rows != (page_size + pool - 1) / pool) return MB_ERR_BAD_SIZE;
-    cudaFuncSetAttribute(attn_pooled_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM);
     const int slices = all_heads ? (K + VH - 1) / VH : 1;
     if (single && (max_query_len != 1 || GROUP > 16)) single = 0;
-    dim3 grid((max_query_len + BM - 1) / BM, (single ? K : K * GROUP) * slices, count);
-    return launch_kernel(attn_pooled_prefill_kernel, grid, 128, PF_SMEM, s, 0, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
+    size_t smem = PF_SMEM;
+    if (single && all_heads && slices > 1 && slices <= 4 && count * K >= by_warp_from) {
+        // every slice in one CTA: the value buffer holds all K heads' blocks, if that fits beside queries and keys.  Only where
+        // requests x kv heads still fill the device (`by_warp_from` CTAs, twice the SMs by default): a CTA then walks its blocks
+        // with loads four times as large, and with
+        // few requests that latency counts for more than the keys read once instead of four times (measured at 4B sizes: batch
+        // 64, 526 -> 425 us a call; batch 8, 73 -> 107 us)
+        const size_t wide = (size_t)(BM * LDK + 2 * BN * LDK + K * BN * LDV) * 2;
+        if (wide <= 200 * 1024) { single = 2; smem = wide > smem ? wide : smem; }
+    }
+    cudaFuncSetAttribute(attn_pooled_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    dim3 grid((max_query_len + BM - 1) / BM, single == 2 ? K : (single ? K : K * GROUP) * slices, count);
+    return launch_kernel(attn_pooled_prefill_kernel, grid, 128, smem, s, 0, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
                          (const bf16*)k_pool, (const bf16*)v_pool, parts, (bf16*)out, block_table, max_pages, cu_tokens, seq_lens, first_req, K,
                          shift, scale, cap, window, pool, pool_rows, all_heads, single);
 }

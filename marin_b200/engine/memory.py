@@ -62,12 +62,14 @@ def workspace_bytes(model, dtype: torch.dtype, token_budget: int, max_batch: int
     from ..parts.base import element_size
 
     size = element_size(dtype)
-    widest = 0
+    widest = extra = 0
     for part in model.parts():
         width = sum(int(s.shape[0]) for s in part.tensor_specs() if s.role == "matrix" and len(s.shape) == 2)
         widest = max(widest, width)
+        # what a part keeps per token beside its products' rows (a mixer that sums every head over every kv head's values)
+        extra = max(extra, int(part.workspace_per_token(dtype)) if hasattr(part, "workspace_per_token") else 0)
     hidden, vocab = model.spec.hidden_size, model.spec.vocab_size
-    per_token = 4 * hidden * (1 + max(1, int(getattr(model.spec, "streams", 0)))) + size * (2 * hidden + 2 * widest)
+    per_token = 4 * hidden * (1 + max(1, int(getattr(model.spec, "streams", 0)))) + size * (2 * hidden + 2 * widest) + extra
     logits = 4 * vocab * max_batch
     graphs = sum(b * (4 * vocab + per_token) for b in graph_sizes)
     scratch = 96 << 20

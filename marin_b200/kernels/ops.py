@@ -1719,7 +1719,7 @@ def attention_pooled(q, k_cache, v_cache, k_pool, v_pool, out, ctx, block_table,
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(k_pool), _ptr(v_pool), _ptr(parts), _ptr(out), _ptr(block_table),
             _c_int(block_table.shape[1]), _ptr(ctx.cu_tokens), _ptr(ctx.seq_lens), _c_int(0), _c_int(ctx.num_requests),
             _c_int(ctx.max_query_len), _c_int(K), _c_int(page_size), _c_float(scale), _c_float(softcap or 0.0), _c_int(window), _c_int(pool),
-            _c_int(rows), _c_int(int(talk is not None)), _c_int(int(ctx.max_query_len == 1 and ctx.num_decode == ctx.num_requests)), _stream()),
+            _c_int(rows), _c_int(int(talk is not None)), _c_int(int(ctx.max_query_len == 1 and ctx.num_decode == ctx.num_requests)), _c_int(POOLED_BY_WARP_FROM), _stream()),
             "attention (window and pooled blocks, tensor cores)")
     if plain_tokens > 0:
         if launch_log is not None:
@@ -1736,8 +1736,11 @@ def attention_pooled(q, k_cache, v_cache, k_pool, v_pool, out, ctx, block_table,
                                                       _stream()), "heads' weights mixed")
 
 
-#: bf16 prompt portions of attention over a window and pooled blocks go to the tensor-core kernel where the head layout allows
+#: bf16 attention over a window and pooled blocks goes to the tensor-core kernel where the head layout allows
 use_fast_pooled_attention = True
+#: single-token steps with mixed weights: from this many (request, kv head) CTAs on, a CTA takes every pair of value heads, a warp
+#: each, over one copy of the keys (fewer, larger CTAs: it pays once they still fill the device twice)
+POOLED_BY_WARP_FROM = 2 * SM_COUNT
 
 
 def fast_pooled_attention_supported(dtype, H: int, K: int, d: int, dv: int) -> bool:

@@ -718,6 +718,11 @@ class PooledAttention(Mixer):
         values = (self.kv_heads if self.talk else 1) * self.v_head_dim
         return super().flops(tokens, pairs) + 2.0 * pairs * self.heads * (self.head_dim + values)
 
+    def workspace_per_token(self, dtype) -> int:
+        """Bytes a step keeps per token beside the products' rows: with mixed weights, every head's float32 sum over every kv
+        head's values."""
+        return 4 * self.heads * self.kv_heads * self.v_head_dim if self.talk else 0
+
     def kernel_jobs(self, dtype) -> Dict[str, tuple]:
         return ops.pooled_attention_jobs(dtype, self.heads, self.kv_heads, self.head_dim, self.v_head_dim)
 
@@ -781,6 +786,9 @@ class ShiftedMixer(Mixer):
         jobs = ops.library_jobs("mb_activations")
         jobs.update(self.inner.kernel_jobs(dtype))
         return jobs
+
+    def workspace_per_token(self, dtype) -> int:
+        return self.inner.workspace_per_token(dtype) if hasattr(self.inner, "workspace_per_token") else 0
 
     def decode_plan_key(self):
         return self.inner.decode_plan_key()

@@ -202,6 +202,23 @@ def test_one_key_stands_out(dtype, back):
         close(got[-24:], want[-24:], dtype, f"back {back}, cuts {cuts[:3]}")
 
 
+def test_single_tokens_with_every_pair_of_value_heads_in_one_block(monkeypatch):
+    """The single-token form that large batches use (a CTA takes all value heads, a warp a pair): forced here for one request."""
+    from marin_b200.kernels import ops
+
+    rt, hidden, T = runtime("bfloat16"), 64, 150
+    m = _attn(8, 4, 32, 128, 0.2, size=40, pool=8, rot={"base": 100.0, "dims": 16}, softcap=10.0)
+    assert ops.pooled_value_heads(4, 128) == 2
+    w = attention_weights(hidden, m, 21)
+    x = bf(torch.randn(T, hidden, generator=torch.Generator().manual_seed(22)))
+    want = plain.pooled_window_attention(x.double(), {k: v.double() for k, v in w.items()}, "m.mix", m, 1e-5)
+    part = build_mixer("attention", m, hidden, 1e-5, rt, w)
+    for limit in (1, 1 << 30):
+        monkeypatch.setattr(ops, "POOLED_BY_WARP_FROM", limit)
+        runner = harness([part.cache_need()], rt, page=16)
+        close(feed([part], runner, x.to(rt.dtype), [30] + [1] * (T - 30))[0], want, "bfloat16", f"from {limit} CTAs on")
+
+
 def test_pooled_rows_live_in_the_pages_and_are_given_back_with_them():
     """Pages, their pooled rows and state slots are handed to the next request: a second request in the places of a first one
     gets what it gets alone in a fresh cache."""
