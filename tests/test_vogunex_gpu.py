@@ -290,6 +290,30 @@ def test_latent_attention_alone(dtype, m):
         runner.cache.check()
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("back", [0, 1, 19, 20, 21, 40, 160])
+@pytest.mark.parametrize("sign", [1.0, -1.0])
+def test_one_latent_row_stands_out_at_the_windows_edge(dtype, back, sign):
+    """The shared key part is not normed, so a row whose input is thirty times the others' has a key part thirty times as
+    long: with one sign or the other its score with the last query towers over the rest.  With a window of 20 it is the last
+    position inside (back 19), the first outside (20), far outside, or the query's own: a kernel that is one position off
+    at the edge, or that looks into pages the window has given back, is wrong by far more than any tolerance."""
+    rt, hidden, T = runtime(dtype), 64, 200
+    m = _latent(4, 32, 16, 32, 64, 32, 0.3, 100.0, size=20)
+    w = latent_weights(hidden, m, 31)
+    g = torch.Generator().manual_seed(back)
+    x = torch.randn(T, hidden, generator=g)
+    x[T - 1 - back] = sign * 30.0 * torch.randn(hidden, generator=g)
+    x = bf(x)
+    want = plain.latent_attention(x.double(), {k: v.double() for k, v in w.items()}, "m.mix", m, 1e-5)
+    part = build_mixer("latent_attention", m, hidden, 1e-5, rt, w)
+    for cuts in ([T], [T - 30] + [1] * 30, portions(T, [16, 2, 5])):
+        # (in small portions the request never holds more than the window's pages and those of the portion)
+        runner = harness([part.cache_need()], rt, page=16, pages=20 if max(cuts) > 16 else 4)
+        got = feed([part], runner, x.to(rt.dtype), cuts)[0]
+        close(got[-40:], want[-40:], dtype, f"back {back}, cuts {cuts[:3]}")
+
+
 def test_a_latent_window_gives_its_pages_back():
     rt, hidden, T = runtime("float32"), 64, 120
     m = LATENTS[0]
